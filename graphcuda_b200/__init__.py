@@ -1,0 +1,22 @@
+"""B200-native GCN layer engine with the API of GraphCUDA
+(src/graphcuda/__init__.py:20-28 of the reference): ``GCNConv`` plus the
+operator functions ``matmul1..4``, ``gemm_cublas``, ``spmm_cusparse``.
+
+Importing the package needs the built C-ABI library
+(``python -m graphcuda_b200.build``); there is no fallback path.
+"""
+from . import _lib
+
+_lib.lib()  # fail loudly at import when the CUDA library is missing
+
+from . import _graphcuda  # noqa: E402
+from ._graphcuda import (gemm_cublas, matmul1, matmul2, matmul3, matmul4,  # noqa: E402
+                         spmm_cusparse)
+from .adjacency import (CSRAdjacency, DenseAdjacency, as_adjacency, gcn_norm,  # noqa: E402
+                        normalized_adjacency)
+from .gcn import GCNConv, GCNConvFunction  # noqa: E402
+from .ops import gemm, get_default_precision, set_default_precision  # noqa: E402
+
+cpp_ext = _graphcuda
+
+__all__ = ["GCNConv", "matmul1", "matmul2", "matmul3", "matmul4", "gemm_cublas", "spmm_cusparse"]

@@ -1,0 +1,299 @@
+"""Adjacency handling: CSR (int32) device storage, its SpMM plan, conversion
+from the layouts the reference API is called with, and GCN normalisation.
+
+The reference's layer takes the normalised adjacency as a torch tensor: sparse
+COO with int64 indices in the shipped extension
+(src/graphcuda/cuda/spmm_cusparse.cu:5-6,33-41), dense in its ATen twin and in
+the README (src/graphcuda/cpp/gcn.cpp:10).  Here every sparse form is turned
+once into an int32 CSR plus a long-row plan and cached on the tensor's
+identity, so a training loop that passes the same ``adj`` every step pays the
+conversion once.
+"""
+from __future__ import annotations
+
+import threading
+import weakref
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .ops import _require, _stream, arena, EPI_RELU, EPI_ACCUMULATE
+
+
+class CSRAdjacency:
+    """int32 CSR on one device, with the SpMM plan and the symmetry verdict."""
+
+    def __init__(self, rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, shape, *,
+                 symmetric: Optional[bool] = None, build_plan: bool = True):
+        _require(rowptr.is_cuda and col.is_cuda and val.is_cuda, "CSR arrays must be CUDA tensors")
+        _require(rowptr.dtype == torch.int32 and col.dtype == torch.int32, "rowptr/col must be int32")
+        _require(val.dtype == torch.float32, "CSR values must be float32")
+        _require(rowptr.numel() == shape[0] + 1, "rowptr must have M+1 entries")
+        _require(col.numel() == val.numel(), "col and val must have the same length")
+        self.rowptr = rowptr.contiguous()
+        self.col = col.contiguous()
+        self.val = val.contiguous()
+        self.shape = (int(shape[0]), int(shape[1]))
+        self.nnz = int(col.numel())
+        self.device = rowptr.device
+        self._symmetric = symmetric
+        self.plan = None
+        if build_plan and self.shape[0] > 0:
+            self._build_plan()
+
+    def _build_plan(self) -> None:
+        L = _lib.lib()
+        M = self.shape[0]
+        nbytes = L.gc_spmm_plan_bytes(M)
+        plan = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            st = L.gc_spmm_plan_build(self.rowptr.data_ptr(), M, plan.data_ptr(), nbytes, _stream(self.device))
+        _lib.check(st, "gc_spmm_plan_build")
+        self.plan = plan
+
+    @property
+    def symmetric(self) -> bool:
+        """Whether A == A^T bit for bit (decides if the layer may aggregate on
+        the output side; the reference multiplies by A in the backward pass,
+        never A^T: src/graphcuda/cuda/gcn.cu:49)."""
+        if self._symmetric is None:
+            if self.shape[0] != self.shape[1]:
+                self._symmetric = False
+            else:
+                out = torch.empty(1, dtype=torch.int32, device=self.device)
+                with torch.cuda.device(self.device):
+                    st = _lib.lib().gc_csr_is_symmetric(self.rowptr.data_ptr(), self.col.data_ptr(),
+                                                        self.val.data_ptr(), self.shape[0], out.data_ptr(),
+                                                        _stream(self.device))
+                _lib.check(st, "gc_csr_is_symmetric")
+                self._symmetric = bool(out.item())
+        return self._symmetric
+
+    def plan_counts(self):
+        """(long rows, segments) of the plan -- a device read, for tests and reports."""
+        if self.plan is None:
+            return (0, 0)
+        hdr = self.plan[:8].view(torch.int32).cpu()
+        return int(hdr[0]), int(hdr[1])
+
+    # -- products -----------------------------------------------------------
+    def matmul(self, H: torch.Tensor, *, bias: Optional[torch.Tensor] = None, relu: bool = False,
+               want_mask: bool = False, accumulate_into: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None):
+        """Y = A @ H (+bias)(ReLU).  Returns Y or (Y, mask)."""
+        _require(H.dim() == 2, "B must be 2D")
+        _require(H.size(0) == self.shape[1], "A.cols must match B.rows")
+        _require(H.is_cuda and H.device == self.device, "A and B must be CUDA tensors on the same device")
+        _require(H.dtype == torch.float32, "B must be float32")
+        if H.stride(1) != 1 or (H.size(0) > 1 and H.stride(0) < H.size(1)):
+            H = H.contiguous()
+        M, K = self.shape
+        F = H.size(1)
+        dev = self.device
+        epi = EPI_RELU if relu else 0
+        if accumulate_into is not None:
+            out = accumulate_into
+            epi |= EPI_ACCUMULATE
+        if out is None:
+            out = torch.empty((M, F), dtype=torch.float32, device=dev)
+        _require(tuple(out.shape) == (M, F) and out.dtype == torch.float32 and out.is_contiguous(),
+                 "out has the wrong shape, dtype or layout")
+        mask = torch.empty((M, F), dtype=torch.float32, device=dev) if want_mask else None
+        if bias is not None:
+            _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == F, "bias must be float32 [F]")
+            bias = bias.contiguous()
+        if M == 0 or F == 0:
+            return (out, mask) if want_mask else out
+        L = _lib.lib()
+        with torch.cuda.device(dev):
+            plan_ptr = self.plan.data_ptr() if self.plan is not None else None
+            scratch = None
+            sbytes = 0
+            if self.plan is not None:
+                sbytes = L.gc_spmm_scratch_bytes(self.nnz, F)
+                scratch = arena.get("spmm", sbytes, dev)
+            ldh = H.stride(0) if H.size(0) > 1 else max(F, 1)
+            st = L.gc_spmm_csr_f32(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
+                                   H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None, epi,
+                                   out.data_ptr(), F, mask.data_ptr() if mask is not None else None, plan_ptr,
+                                   scratch.data_ptr() if scratch is not None else None,
+                                   scratch.numel() if scratch is not None else 0, _stream(dev))
+        _lib.check(st, "gc_spmm_csr_f32")
+        return (out, mask) if want_mask else out
+
+    def to_sparse_coo(self) -> torch.Tensor:
+        counts = (self.rowptr[1:] - self.rowptr[:-1]).long()
+        rows = torch.repeat_interleave(torch.arange(self.shape[0], device=self.device), counts)
+        idx = torch.stack([rows, self.col.long()])
+        return torch.sparse_coo_tensor(idx, self.val, self.shape, device=self.device, is_coalesced=True)
+
+
+class DenseAdjacency:
+    """A dense normalised adjacency (the README / ATen-twin calling convention,
+    src/graphcuda/cpp/gcn.cpp:10).  Products run on the dense GEMM path."""
+
+    def __init__(self, A: torch.Tensor, symmetric: Optional[bool] = None):
+        _require(A.dim() == 2 and A.is_cuda and A.dtype == torch.float32, "dense adjacency must be a float32 CUDA matrix")
+        self.A = A
+        self.shape = tuple(A.shape)
+        self.device = A.device
+        self._symmetric = symmetric
+
+    @property
+    def symmetric(self) -> bool:
+        if self._symmetric is None:
+            self._symmetric = self.shape[0] == self.shape[1] and bool(torch.equal(self.A, self.A.t()))
+        return self._symmetric
+
+    def matmul(self, H: torch.Tensor, *, bias=None, relu=False, want_mask=False, accumulate_into=None, out=None,
+               precision=None):
+        from .ops import gemm
+        _require(accumulate_into is None, "accumulate is not available on the dense path")
+        return gemm(self.A, H, bias=bias, relu=relu, want_mask=want_mask, precision=precision, out=out)
+
+
+# ---------------------------------------------------------------- conversion
+def csr_from_sorted_coo(rows: torch.Tensor, cols: torch.Tensor, vals: torch.Tensor, shape, *,
+                        symmetric: Optional[bool] = None) -> CSRAdjacency:
+    """CSR from a *coalesced* COO triple (rows ascending, then cols; int64)."""
+    dev = rows.device
+    M = int(shape[0])
+    nnz = int(rows.numel())
+    _require(nnz < 2**31 - 1 and M < 2**31 - 1 and int(shape[1]) < 2**31 - 1, "matrix too large for int32 CSR")
+    L = _lib.lib()
+    rowptr = torch.empty(M + 1, dtype=torch.int32, device=dev)
+    col32 = torch.empty(nnz, dtype=torch.int32, device=dev)
+    rows = rows.contiguous()
+    cols = cols.contiguous()
+    with torch.cuda.device(dev):
+        s = _stream(dev)
+        _lib.check(L.gc_coo_rows_to_rowptr(rows.data_ptr(), nnz, M, rowptr.data_ptr(), s), "gc_coo_rows_to_rowptr")
+        _lib.check(L.gc_narrow_i64_i32(cols.data_ptr(), col32.data_ptr(), nnz, s), "gc_narrow_i64_i32")
+    return CSRAdjacency(rowptr, col32, vals.contiguous(), shape, symmetric=symmetric)
+
+
+_cache_lock = threading.Lock()
+_cache: dict = {}
+
+
+def _cache_key(t: torch.Tensor):
+    if t.layout == torch.sparse_coo:
+        v = t._values()
+        i = t._indices()
+        return ("coo", v.data_ptr(), i.data_ptr(), v._version, i._version, tuple(t.shape), t._nnz(), t.is_coalesced())
+    if t.layout == torch.sparse_csr:
+        v = t.values()
+        return ("csr", v.data_ptr(), t.crow_indices().data_ptr(), t.col_indices().data_ptr(), v._version,
+                tuple(t.shape))
+    return ("dense", t.data_ptr(), t._version, tuple(t.shape), t.stride())
+
+
+def as_adjacency(adjm, *, symmetric: Optional[bool] = None):
+    """CSRAdjacency / DenseAdjacency for whatever the caller passed as ``adjm``.
+
+    Accepts a CSRAdjacency, a (rowptr, col, val[, shape]) tuple, or a torch
+    tensor with strided, sparse_coo or sparse_csr layout.  Results for tensors
+    are cached on (storage pointer, version counter, shape); the cache holds a
+    weak reference to the tensor and drops the entry when the tensor dies.
+    """
+    if isinstance(adjm, (CSRAdjacency, DenseAdjacency)):
+        return adjm
+    if isinstance(adjm, (tuple, list)):
+        rowptr, col, val = adjm[:3]
+        shape = adjm[3] if len(adjm) > 3 else (rowptr.numel() - 1, rowptr.numel() - 1)
+        return CSRAdjacency(rowptr, col, val, shape, symmetric=symmetric)
+    _require(isinstance(adjm, torch.Tensor), "adjacency must be a tensor, a CSR tuple or a CSRAdjacency")
+    _require(adjm.dim() == 2, "A must be 2D")
+    _require(adjm.is_cuda, "A and B must be CUDA tensors")
+    _require(adjm.dtype == torch.float32, "A values must be float32")
+    key = _cache_key(adjm)
+    with _cache_lock:
+        hit = _cache.get(key)
+        if hit is not None and hit[0]() is not None:
+            return hit[1]
+    if adjm.layout == torch.sparse_coo:
+        t = adjm if adjm.is_coalesced() else adjm.coalesce()
+        idx = t._indices()
+        _require(idx.dtype == torch.int64, "A indices must be int64")
+        adj = csr_from_sorted_coo(idx[0], idx[1], t._values(), t.shape, symmetric=symmetric)
+    elif adjm.layout == torch.sparse_csr:
+        adj = CSRAdjacency(adjm.crow_indices().to(torch.int32), adjm.col_indices().to(torch.int32), adjm.values(),
+                           adjm.shape, symmetric=symmetric)
+    elif adjm.layout == torch.strided:
+        adj = DenseAdjacency(adjm, symmetric=symmetric)
+    else:
+        raise RuntimeError(f"unsupported adjacency layout {adjm.layout}")
+    with _cache_lock:
+        if len(_cache) > 64:
+            for k in [k for k, v in _cache.items() if v[0]() is None]:
+                _cache.pop(k, None)
+        try:
+            _cache[key] = (weakref.ref(adjm), adj)
+        except TypeError:
+            pass
+    return adj
+
+
+def clear_cache() -> None:
+    with _cache_lock:
+        _cache.clear()
+
+
+# ---------------------------------------------------------------- normalisation
+def gcn_norm(edge_index: torch.Tensor, num_nodes: int) -> torch.Tensor:
+    """Symmetric GCN edge weights deg^-1/2[row] * deg^-1/2[col] for an edge list
+    that already holds the self-loops (deg counted on the target index), as
+    torch_geometric's gcn_norm computes them for unit weights at the
+    reference's call site tests/gcn/graphcuda_impl.py:28.  Bit-exact against
+    the torch CPU formula."""
+    _require(edge_index.is_cuda and edge_index.dtype == torch.int64 and edge_index.dim() == 2
+             and edge_index.size(0) == 2, "edge_index must be a CUDA int64 [2, E] tensor")
+    dev = edge_index.device
+    E = edge_index.size(1)
+    row = edge_index[0].contiguous()
+    col = edge_index[1].contiguous()
+    w = torch.empty(E, dtype=torch.float32, device=dev)
+    deg = torch.empty(max(num_nodes, 1), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.lib().gc_gcn_norm_f32(row.data_ptr(), col.data_ptr(), E, num_nodes, deg.data_ptr(), w.data_ptr(),
+                                        _stream(dev))
+    _lib.check(st, "gc_gcn_norm_f32")
+    return w
+
+
+def normalized_adjacency(edge_index: torch.Tensor, num_nodes: int, *, add_self_loops: bool = True,
+                         symmetric: Optional[bool] = None) -> CSRAdjacency:
+    """Edge list -> (+self-loops) -> symmetric normalisation -> coalesced int32
+    CSR, the whole preprocessing of tests/gcn/graphcuda_impl.py:27-38 on the
+    GPU.  The (row, col) ordering uses torch.sort on the device; degree,
+    normalisation, de-duplication and CSR assembly are this library's kernels.
+    """
+    _require(edge_index.is_cuda and edge_index.dtype == torch.int64, "edge_index must be a CUDA int64 tensor")
+    dev = edge_index.device
+    if add_self_loops:
+        loops = torch.arange(num_nodes, device=dev, dtype=torch.int64)
+        edge_index = torch.cat([edge_index, torch.stack([loops, loops])], dim=1)
+    w = gcn_norm(edge_index, num_nodes)
+    key = edge_index[0] * num_nodes + edge_index[1]
+    key, order = torch.sort(key, stable=True)
+    row = edge_index[0][order].contiguous()
+    col = edge_index[1][order].contiguous()
+    w = w[order].contiguous()
+    E = row.numel()
+    L = _lib.lib()
+    head = torch.empty(max(E, 1), dtype=torch.int32, device=dev)
+    nnz_dev = torch.empty(1, dtype=torch.int64, device=dev)
+    wsb = L.gc_csr_build_workspace_bytes(E)
+    ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        s = _stream(dev)
+        _lib.check(L.gc_csr_count_unique(row.data_ptr(), col.data_ptr(), E, head.data_ptr(), nnz_dev.data_ptr(),
+                                         ws.data_ptr(), wsb, s), "gc_csr_count_unique")
+        nnz = int(nnz_dev.item())
+        rowptr = torch.empty(num_nodes + 1, dtype=torch.int32, device=dev)
+        ccol = torch.empty(nnz, dtype=torch.int32, device=dev)
+        cval = torch.empty(nnz, dtype=torch.float32, device=dev)
+        _lib.check(L.gc_csr_fill(row.data_ptr(), col.data_ptr(), w.data_ptr(), E, num_nodes, head.data_ptr(),
+                                 rowptr.data_ptr(), ccol.data_ptr(), cval.data_ptr(), s), "gc_csr_fill")
+    return CSRAdjacency(rowptr, ccol, cval, (num_nodes, num_nodes), symmetric=symmetric)

@@ -1,0 +1,38 @@
+// Library-level entry points: version, status text, thread-local error text.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace {
+thread_local char g_last_error[512] = {0};
+}
+
+namespace gc {
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+}  // namespace gc
+
+extern "C" {
+
+int gc_abi_version(void) { return 1; }
+
+const char* gc_last_error(void) { return g_last_error; }
+
+const char* gc_status_string(int status) {
+  switch (status) {
+    case GC_OK: return "ok";
+    case GC_ERR_INVALID: return "invalid argument";
+    case GC_ERR_UNSUPPORTED: return "unsupported configuration";
+    case GC_ERR_CUDA: return "CUDA error";
+    case GC_ERR_WORKSPACE: return "workspace missing or too small";
+    case GC_ERR_DEVICE_FLAG: return "a device-side bounded wait ran out";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"

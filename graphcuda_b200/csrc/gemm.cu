@@ -1,0 +1,90 @@
+// gc_gemm_f32: argument checks and the choice between the CUDA-core and the
+// tensor-core back end.  Replaces the reference's GEMM entry points
+// (src/graphcuda/cuda/gemm_cublas.cu:3-55, matmul1.cu:27-61, matmul2.cu:65-100,
+// matmul3.cu:194-243, matmul4.cu:209-265).
+#include "common.cuh"
+#include "gemm_internal.cuh"
+
+namespace {
+
+int resolve(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+            int precision) {
+  if (precision == GC_PREC_FP32_SIMT) return GC_PREC_FP32_SIMT;
+  const bool tc_ok = gc::tc_supported(ta, tb, M, N, K, lda, ldb, ldc);
+  if (precision == GC_PREC_TF32X3 || precision == GC_PREC_TF32) {
+    if (!tc_ok)
+      return gc::fail(GC_ERR_UNSUPPORTED,
+                      "tensor-core GEMM needs 16-byte aligned row pitches for operands read in place "
+                      "(lda %% 4 == 0 when transA == 0, ldb %% 4 == 0 when transB == 1) and non-empty sizes");
+    return precision;
+  }
+  if (precision != GC_PREC_AUTO) return gc::fail(GC_ERR_INVALID, "unknown precision %d", precision);
+  if (!tc_ok) return GC_PREC_FP32_SIMT;
+  // Small problems are launch-bound and stay on the CUDA cores (bit-stable);
+  // so do few-tile / huge-K shapes (weight gradients), which the CUDA-core
+  // kernel splits along K.
+  const double flops = 2.0 * double(M) * double(N) * double(K);
+  if (flops < double(1ull << 30) || M < 512) return GC_PREC_FP32_SIMT;
+  const int64_t tiles = gc::ceil_div(M, 128) * gc::ceil_div(N, 256);
+  if (tiles < 32 && K >= 8192) return GC_PREC_FP32_SIMT;
+  return GC_PREC_TF32X3;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gc_gemm_resolve_precision(int transA, int transB, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                              int64_t ldc, int precision) {
+  return resolve(transA != 0, transB != 0, M, N, K, lda, ldb, ldc, precision);
+}
+
+size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int64_t K, int precision) {
+  if (M <= 0 || N <= 0 || K < 0) return 256;
+  // AUTO may resolve either way depending on leading dimensions: report the larger.
+  size_t simt = gc::simt_workspace_bytes(M, N, K);
+  size_t tc3 = gc::tc_workspace_bytes(transA != 0, transB != 0, M, N, K, 3);
+  size_t tc1 = gc::tc_workspace_bytes(transA != 0, transB != 0, M, N, K, 1);
+  switch (precision) {
+    case GC_PREC_FP32_SIMT: return std::max<size_t>(simt, 256);
+    case GC_PREC_TF32X3: return tc3;
+    case GC_PREC_TF32: return tc1;
+    default: return std::max(std::max(simt, tc3), size_t(256));
+  }
+}
+
+int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float* C, int64_t ldc, const float* bias, int epilogue, float* mask,
+                int precision, void* workspace, size_t workspace_bytes, void* stream) {
+  GC_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gc_gemm_f32: negative size");
+  GC_REQUIRE(M < INT32_MAX && N < INT32_MAX && K < INT32_MAX, "gc_gemm_f32: size out of int32 range");
+  GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_TRANSPOSED_OUT)) == 0, "gc_gemm_f32: unknown epilogue bits");
+  if (M == 0 || N == 0) return GC_OK;
+  const bool ta = transA != 0, tb = transB != 0;
+  const bool tr = (epilogue & GC_EPI_TRANSPOSED_OUT) != 0;
+  GC_REQUIRE(C, "gc_gemm_f32: null C");
+  GC_REQUIRE(K == 0 || (A && B), "gc_gemm_f32: null operand");
+  GC_REQUIRE(lda >= (ta ? M : K), "gc_gemm_f32: lda too small");
+  GC_REQUIRE(ldb >= (tb ? K : N), "gc_gemm_f32: ldb too small");
+  GC_REQUIRE(ldc >= (tr ? M : N), "gc_gemm_f32: ldc too small");
+  gc::GemmEpilogue ep{bias, mask, (epilogue & GC_EPI_RELU) ? 1 : 0, tr ? 1 : 0};
+  cudaStream_t st = gc::as_stream(stream);
+  int prec = (K == 0) ? GC_PREC_FP32_SIMT : resolve(ta, tb, M, N, K, lda, ldb, ldc, precision);
+  if (prec < 0) return prec;
+  if (prec == GC_PREC_FP32_SIMT)
+    return gc::gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, ep, workspace, workspace_bytes, st);
+  return gc::gemm_tc(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, ep, prec == GC_PREC_TF32X3 ? 3 : 1, workspace,
+                     workspace_bytes, st);
+}
+
+int gc_gemm_check_flag(const void* workspace, void* stream) {
+  GC_REQUIRE(workspace, "gc_gemm_check_flag: null workspace");
+  int h = 0;
+  cudaError_t e = cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, gc::as_stream(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(gc::as_stream(stream));
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "gc_gemm_check_flag: %s", cudaGetErrorString(e));
+  if (h != 0) return gc::fail(GC_ERR_DEVICE_FLAG, "a tensor-core GEMM kernel gave up a bounded wait");
+  return GC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,555 @@
+// fp32-in / fp32-out GEMM on the 5th-generation tensor cores (sm_100a).
+//
+// C[M,N] = A[M,K] * Bt[N,K]^T with both operands K-major in shared memory,
+// kind::tf32 MMAs issued by one thread per CTA, fp32 accumulators in TMEM.
+// Takes over cublasSgemm as the reference wraps it
+// (src/graphcuda/cuda/gemm_cublas.cu:37-48) for the large products of the GCN
+// layer (src/graphcuda/cuda/gcn.cu:15,43,46).
+//
+// fp32 semantics on a TF32 pipe ("three-pass" mode): the tensor core reads the
+// upper 19 bits of each fp32 word, so x_hi = trunc19(x) comes for free and
+// x_lo = x - x_hi is exact in fp32.  D = A_lo*B_hi + A_hi*B_lo + A_hi*B_hi
+// restores ~21 bits of operand precision.  B_lo (weights: small, reused by
+// every tile) is produced once by a pre-pass into the workspace; A_lo is made
+// on the fly by four converter warps from the tile TMA just landed, so A is
+// read from HBM exactly once.
+//
+// CTA = 12 warps, persistent over 128 x BN output tiles:
+//   warp 0      TMA producer (one lane)           full[s]  <- bytes landed
+//   warp 1      MMA issuer (one lane)             empty[s] <- tcgen05.commit
+//   warp 2      TMEM allocator / idle
+//   warps 4-7   epilogue: tcgen05.ld -> bias/ReLU/mask -> global
+//   warps 8-11  converter: A tile -> A_lo tile    conv[s]
+// Two TMEM accumulators (2 x BN columns) let the epilogue of tile i overlap
+// the main loop of tile i+1.
+//
+// Every wait is bounded: a wait that runs out raises a CTA-wide abort flag and
+// a word in global memory, all roles leave their loops, outstanding TMA
+// copies are drained (bounded) and TMEM is released before the CTA exits.
+#include "common.cuh"
+#include "gemm_internal.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;      // fp32 per 128-byte swizzle row
+constexpr int UMMA_K = 8;   // K of one kind::tf32 instruction
+constexpr int kThreads = 384;
+constexpr uint32_t kWaitLimit = 1u << 24;
+
+// ------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another
+// ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_s) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 128) {
+      __nanosleep(64);
+      if (*abort_s) return false;
+    }
+  }
+  *abort_s = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of
+// 128 bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor
+// version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);
+  d |= uint64_t(1024u >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+  return (1u << 4)                    // D format: F32
+         | (2u << 7)                  // A format: TF32
+         | (2u << 10)                 // B format: TF32
+         | (uint32_t(bn >> 3) << 17)  // N / 8
+         | (uint32_t(BM >> 4) << 24); // M / 16
+}
+
+struct TcParams {
+  int M, N, K;
+  float* C;
+  int64_t ldc;
+  gc::GemmEpilogue ep;
+  int* flag;  // global word set when a wait ran out
+  int vec_store;  // rows of C are 16-byte aligned
+};
+
+template <int BN, int PASSES>
+struct Cfg {
+  static constexpr int kABytes = BM * BK * 4;
+  static constexpr int kBBytes = BN * BK * 4;
+  static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kABytes + kBBytes);
+  static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert(kStages >= 2, "need at least two stages");
+};
+
+template <int BN, int PASSES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const __grid_constant__ CUtensorMap mapBlo, TcParams p) {
+  using C_ = Cfg<BN, PASSES>;
+  constexpr int S = C_::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  // stage layout: [A | B | A_lo | B_lo]
+  auto sA = [&](int s) { return base + s * C_::kStageBytes; };
+  auto sB = [&](int s) { return base + s * C_::kStageBytes + C_::kABytes; };
+  auto sAlo = [&](int s) { return base + s * C_::kStageBytes + C_::kABytes + C_::kBBytes; };
+  auto sBlo = [&](int s) { return base + s * C_::kStageBytes + 2 * C_::kABytes + C_::kBBytes; };
+  const uint32_t bars = base + S * C_::kStageBytes;
+  auto bar_full = [&](int s) { return bars + 8 * s; };
+  auto bar_empty = [&](int s) { return bars + 8 * (S + s); };
+  auto bar_conv = [&](int s) { return bars + 8 * (2 * S + s); };
+  auto bar_tfull = [&](int b) { return bars + 8 * (3 * S + b); };
+  auto bar_tempty = [&](int b) { return bars + 8 * (3 * S + 2 + b); };
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int num_tiles = tiles_m * tiles_n;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+      mbar_init(bar_conv(s), 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull(b), 1);
+      mbar_init(bar_tempty(b), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 2) tmem_alloc(smem_u32(&tmem_base_s), C_::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_p = &abort_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_p)) { ok = false; break; }
+          mbar_expect_tx(bar_full(s), C_::kABytes + (PASSES == 3 ? 2 : 1) * C_::kBBytes);
+          tma_load_2d(sA(s), &mapA, kb * BK, m0, bar_full(s));
+          tma_load_2d(sB(s), &mapB, kb * BK, n0, bar_full(s));
+          if (PASSES == 3) tma_load_2d(sBlo(s), &mapBlo, kb * BK, n0, bar_full(s));
+        }
+      }
+      // Drain: every copy issued must have landed before the CTA may exit.
+      // `it` loads were issued; the last min(S, it) of them may be in flight.
+      const uint32_t pending = it < uint32_t(S) ? it : uint32_t(S);
+      for (uint32_t j = 0; j < pending; ++j) {
+        const uint32_t q = it - 1 - j;
+        const uint32_t bar = bar_full(q % S), par = (q / S) & 1u;
+        for (uint32_t i = 0; i < kWaitLimit; ++i) {
+          if (mbar_test(bar, par)) break;
+          __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int b = tcount & 1;
+        const uint32_t bph = (tcount >> 1) & 1u;
+        if (!mbar_wait(bar_tempty(b), bph ^ 1u, abort_p)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(b * BN);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(bar_full(s), ph, abort_p)) { ok = false; break; }
+          if (PASSES == 3 && !mbar_wait(bar_conv(s), ph, abort_p)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = smem_desc_k128(sA(s)), db = smem_desc_k128(sB(s));
+          const uint64_t dal = smem_desc_k128(sAlo(s)), dbl = smem_desc_k128(sBlo(s));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adv = uint64_t((k * UMMA_K * 4) >> 4);  // bytes >> 4 in the address field
+            const uint32_t first = (kb | k) ? 1u : 0u;
+            if (PASSES == 3) {
+              umma_tf32(d_tmem, dal + adv, db + adv, idesc, first);
+              umma_tf32(d_tmem, da + adv, dbl + adv, idesc, 1u);
+              umma_tf32(d_tmem, da + adv, db + adv, idesc, 1u);
+            } else {
+              umma_tf32(d_tmem, da + adv, db + adv, idesc, first);
+            }
+          }
+          umma_commit(bar_empty(s));  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(bar_tfull(b));
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp - 4;  // TMEM lane quarter == warp id % 4
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int b = tcount & 1;
+      const uint32_t bph = (tcount >> 1) & 1u;
+      if (!mbar_wait(bar_tfull(b), bph, abort_p)) { ok = false; break; }
+      tc_fence_after();
+      const int gm = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + uint32_t(c * 32), r);
+        tmem_ld_wait();
+        const int gn0 = n0 + c * 32;
+        if (gn0 >= p.N) continue;  // uniform across the warp
+        if (p.ep.transposed) {
+          // lanes hold consecutive m: a column of C is a contiguous run of C^T
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int gn = gn0 + j;
+            if (gn < p.N && gm < p.M) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, p.C, p.ldc, p.ep);
+          }
+        } else if (gm < p.M) {
+          if (p.vec_store && gn0 + 32 <= p.N) {
+            float* crow = p.C + int64_t(gm) * p.ldc + gn0;
+            float* mrow = p.ep.mask ? p.ep.mask + int64_t(gm) * p.ldc + gn0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                     __uint_as_float(r[j + 3]));
+              if (p.ep.bias) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.ep.bias + gn0 + j));
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              if (p.ep.relu || mrow) {
+                const float4 mk = make_float4(v.x > 0.f ? 1.f : 0.f, v.y > 0.f ? 1.f : 0.f, v.z > 0.f ? 1.f : 0.f,
+                                              v.w > 0.f ? 1.f : 0.f);
+                if (mrow) *reinterpret_cast<float4*>(mrow + j) = mk;
+                if (p.ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
+              }
+              *reinterpret_cast<float4*>(crow + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int gn = gn0 + j;
+              if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, p.C, p.ldc, p.ep);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty(b));
+    }
+  } else if (warp >= 8 && PASSES == 3) {
+    // ------------------------------------------------------------ converter
+    const int ct = threadIdx.x - 256;  // 0..127
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        if (!mbar_wait(bar_full(s), ph, abort_p)) { ok = false; break; }
+        const float4* src = reinterpret_cast<const float4*>(smem + s * C_::kStageBytes);
+        float4* dst = reinterpret_cast<float4*>(smem + s * C_::kStageBytes + C_::kABytes + C_::kBBytes);
+#pragma unroll
+        for (int i = 0; i < C_::kABytes / 16 / 128; ++i) {
+          const float4 v = src[ct + i * 128];
+          float4 lo;
+          lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+          lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+          lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+          lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+          dst[ct + i * 128] = lo;
+        }
+        fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_conv(s));
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 2) tmem_dealloc(tmem_base, C_::kTmemCols);
+  if (threadIdx.x == 0 && abort_s && p.flag) atomicExch(p.flag, 1);
+}
+
+// B_lo = B - trunc19(B) over an R x Kc view.
+__global__ void __launch_bounds__(256)
+split_lo_kernel(const float* __restrict__ src, int64_t lds, float* __restrict__ dst, int64_t ldd, int R, int Kc) {
+  const int64_t total = int64_t(R) * Kc;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+    const int r = int(i / Kc), k = int(i % Kc);
+    const float v = __ldg(src + int64_t(r) * lds + k);
+    dst[int64_t(r) * ldd + k] = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+  }
+}
+
+// out[c][r] = in[r][c] through a 32 x 33 shared tile.
+__global__ void __launch_bounds__(256)
+transpose_kernel(const float* __restrict__ in, int64_t ldin, float* __restrict__ out, int64_t ldout, int R, int Cc) {
+  __shared__ float t[32][33];
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int64_t tiles_c = (Cc + 31) / 32;
+  const int64_t tiles = int64_t((R + 31) / 32) * tiles_c;
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int r0 = int(tile / tiles_c) * 32, c0 = int(tile % tiles_c) * 32;
+    for (int i = ty; i < 32; i += 8)
+      t[i][tx] = (r0 + i < R && c0 + tx < Cc) ? __ldg(in + int64_t(r0 + i) * ldin + c0 + tx) : 0.f;
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+      if (c0 + i < Cc && r0 + tx < R) out[int64_t(c0 + i) * ldout + r0 + tx] = t[tx][i];
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ host
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
+}
+
+// Tensor map over a K-major operand: `rows` rows of `K` fp32, row pitch ld;
+// box = 32 fp32 (128 bytes, the swizzle span) x box_rows.
+int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+  EncodeFn enc = get_encode();
+  if (!enc) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * 4};
+  cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return GC_OK;
+}
+
+inline int64_t round4(int64_t x) { return (x + 3) & ~int64_t(3); }
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+int pick_bn(int64_t N) {
+  if (N <= 64) return 64;
+  if (N <= 128) return 128;
+  const int64_t rem = N % 256;
+  return (rem == 0 || rem > 128) ? 256 : 128;
+}
+
+template <int BN, int PASSES>
+int launch_tc(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mBlo, const TcParams& p,
+              cudaStream_t st) {
+  using C_ = Cfg<BN, PASSES>;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       C_::kSmemBytes);
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const int64_t tiles = gc::ceil_div(p.M, BM) * gc::ceil_div(p.N, BN);
+  const unsigned grid = unsigned(std::min<int64_t>(tiles, gc::kNumSMs));
+  gemm_tf32_kernel<BN, PASSES><<<grid, kThreads, C_::kSmemBytes, st>>>(mA, mB, mBlo, p);
+  return gc::check_launch("gemm_tf32_kernel");
+}
+
+}  // namespace
+
+namespace gc {
+
+bool tc_supported(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc) {
+  (void)ldc;
+  if (M <= 0 || N <= 0 || K <= 0) return false;
+  if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return false;
+  // operands read in place must have 16-byte aligned row pitch; transposed
+  // operands are re-laid into the workspace with a padded pitch
+  if (!ta && (lda % 4 != 0)) return false;
+  if (tb && (ldb % 4 != 0)) return false;
+  return true;
+}
+
+// Workspace layout: [flag: 256 B][A^T (transA)][B^T (!transB)][B_lo (3 passes)]
+size_t tc_workspace_bytes(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int passes) {
+  size_t b = 256;
+  const size_t kp = size_t(round4(K));
+  if (ta) b += align256(size_t(M) * kp * 4);
+  if (!tb) b += align256(size_t(N) * kp * 4);
+  if (passes == 3) b += align256(size_t(N) * kp * 4);
+  return b;
+}
+
+int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+            int64_t ldb, float* C, int64_t ldc, const GemmEpilogue& ep, int passes, void* workspace,
+            size_t workspace_bytes, cudaStream_t st) {
+  if (!workspace || workspace_bytes < tc_workspace_bytes(ta, tb, M, N, K, passes))
+    return fail(GC_ERR_WORKSPACE, "gemm_tc: workspace missing or smaller than gc_gemm_workspace_bytes()");
+  if (!aligned16(workspace)) return fail(GC_ERR_INVALID, "gemm_tc: workspace must be 16-byte aligned");
+  char* ws = static_cast<char*>(workspace);
+  int* flag = reinterpret_cast<int*>(ws);
+  ws += 256;
+  const int64_t kp = round4(K);
+  const unsigned tgrid = kNumSMs * 8;
+  int rc;
+
+  const float* Ak = A;  // K-major view of A: M rows of K
+  int64_t ldak = lda;
+  if (ta) {
+    float* At = reinterpret_cast<float*>(ws);
+    ws += align256(size_t(M) * kp * 4);
+    transpose_kernel<<<tgrid, 256, 0, st>>>(A, lda, At, kp, int(K), int(M));
+    if ((rc = check_launch("transpose A")) != GC_OK) return rc;
+    Ak = At;
+    ldak = kp;
+  }
+  const float* Bk = B;  // K-major view of B: N rows of K
+  int64_t ldbk = ldb;
+  if (!tb) {
+    float* Bt = reinterpret_cast<float*>(ws);
+    ws += align256(size_t(N) * kp * 4);
+    transpose_kernel<<<tgrid, 256, 0, st>>>(B, ldb, Bt, kp, int(K), int(N));
+    if ((rc = check_launch("transpose B")) != GC_OK) return rc;
+    Bk = Bt;
+    ldbk = kp;
+  }
+  const float* Blo = Bk;
+  if (passes == 3) {
+    float* bl = reinterpret_cast<float*>(ws);
+    ws += align256(size_t(N) * kp * 4);
+    split_lo_kernel<<<tgrid, 256, 0, st>>>(Bk, ldbk, bl, kp, int(N), int(K));
+    if ((rc = check_launch("split B")) != GC_OK) return rc;
+    Blo = bl;
+  }
+  if (!aligned16(Ak) || !aligned16(Bk)) return fail(GC_ERR_UNSUPPORTED, "gemm_tc: operand base not 16-byte aligned");
+
+  const int bn = pick_bn(N);
+  CUtensorMap mA, mB, mBlo;
+  if ((rc = make_map(&mA, Ak, M, K, ldak, BM)) != GC_OK) return rc;
+  if ((rc = make_map(&mB, Bk, N, K, ldbk, bn)) != GC_OK) return rc;
+  if ((rc = make_map(&mBlo, Blo, N, K, passes == 3 ? kp : ldbk, bn)) != GC_OK) return rc;
+
+  TcParams p;
+  p.M = int(M);
+  p.N = int(N);
+  p.K = int(K);
+  p.C = C;
+  p.ldc = ldc;
+  p.ep = ep;
+  p.flag = flag;
+  p.vec_store = (!ep.transposed && ldc % 4 == 0 && aligned16(C) && (!ep.mask || aligned16(ep.mask)) &&
+                 (!ep.bias || aligned16(ep.bias)))
+                    ? 1
+                    : 0;
+#define GC_TC(BN_)                                                                 \
+  (passes == 3 ? launch_tc<BN_, 3>(mA, mB, mBlo, p, st) : launch_tc<BN_, 1>(mA, mB, mBlo, p, st))
+  if (bn == 64) return GC_TC(64);
+  if (bn == 128) return GC_TC(128);
+  return GC_TC(256);
+#undef GC_TC
+}
+
+}  // namespace gc

@@ -1,0 +1,98 @@
+"""Layer-level composition of the kernels: one GCN layer forward and backward.
+
+Reference math (src/graphcuda/cuda/gcn.cu:5-52, twin src/graphcuda/cpp/gcn.cpp:4-41):
+    forward   Y  = relu((A X) W)
+    backward  G  = dY * mask;  dW = (A X)^T G;  dX = A (G W^T)
+The reference always aggregates first and recomputes A X in the backward pass.
+Here the aggregation runs on the narrower side -- (A X) W when in <= out,
+A (X W) when out < in and A is symmetric -- the intermediate is kept for the
+backward pass, ReLU/bias/mask are fused into the producing kernel, transposed
+operands are read in place, and dX is skipped when nobody needs it.  For a
+non-symmetric A the aggregate-first order is always used, so the results are
+the reference's (including its use of A rather than A^T for dX, gcn.cu:49).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import ops
+from .ops import _require
+
+
+def _check_layer_args(X, adj, W):
+    _require(X.dim() == 2 and W.dim() == 2, "Inputs must be 2D")
+    _require(X.is_cuda and W.is_cuda, "Inputs must be CUDA tensors")
+    _require(X.dtype == torch.float32 and W.dtype == torch.float32, "Only float32 is supported here")
+    _require(adj.shape[1] == X.size(0), "A.cols must match B.rows")
+    _require(X.size(1) == W.size(0), "A.cols must match B.rows")
+
+
+def choose_order(in_dim: int, out_dim: int, symmetric: bool) -> str:
+    return "transform_first" if (out_dim < in_dim and symmetric) else "aggregate_first"
+
+
+def _adj_matmul(adj, H, precision, **kw):
+    from .adjacency import DenseAdjacency
+    if isinstance(adj, DenseAdjacency):
+        return adj.matmul(H, precision=precision, **kw)
+    return adj.matmul(H, **kw)
+
+
+def layer_forward(X, adj, W, bias: Optional[torch.Tensor], relu: bool, *, want_mask: bool = False,
+                  precision: Optional[str] = None, order: Optional[str] = None):
+    """Returns (Y, mask or None, saved) where saved = (order, intermediate):
+    the intermediate is A X (aggregate_first) or None (transform_first)."""
+    _check_layer_args(X, adj, W)
+    if order is None:
+        order = choose_order(W.size(0), W.size(1), adj.symmetric if W.size(1) < W.size(0) else False)
+    if order == "aggregate_first":
+        AX = _adj_matmul(adj, X, precision)
+        r = ops.gemm(AX, W, bias=bias, relu=relu, want_mask=want_mask, precision=precision)
+        Y, mask = r if want_mask else (r, None)
+        return Y, mask, (order, AX)
+    H = ops.gemm(X, W, precision=precision)
+    r = _adj_matmul(adj, H, precision, bias=bias, relu=relu, want_mask=want_mask)
+    Y, mask = r if want_mask else (r, None)
+    return Y, mask, (order, None)
+
+
+def layer_backward(dY, X, adj, W, relu: bool, Y, saved, *, need_dX: bool = True, need_dW: bool = True,
+                   need_db: bool = False, precision: Optional[str] = None):
+    """Gradients (dX, dW, db) of layer_forward; Y is the saved activation (the
+    ReLU mask is re-derived from it as Y > 0)."""
+    order, AX = saved
+    G = ops.relu_backward(dY, Y) if relu else dY
+    if G.stride(1) != 1:
+        G = G.contiguous()
+    dX = dW = db = None
+    if need_db:
+        db = G.sum(0)
+    if order == "aggregate_first":
+        if need_dW:
+            dW = ops.gemm(AX.t(), G, precision=precision)
+        if need_dX:
+            T = ops.gemm(G, W.t(), precision=precision)
+            dX = _adj_matmul(adj, T, precision)  # A, not A^T: reference gcn.cu:49
+    else:
+        # Y = A (X W), A symmetric: S = A^T G = A G
+        S = _adj_matmul(adj, G, precision)
+        if need_dW:
+            dW = ops.gemm(X.t(), S, precision=precision)
+        if need_dX:
+            dX = ops.gemm(S, W.t(), precision=precision)
+    return dX, dW, db
+
+
+def layer_backward_reference_form(dY, X, adj, W, relu: bool, mask, *, precision: Optional[str] = None):
+    """(dX, dW) from exactly what the reference's backward entry point receives
+    (no saved intermediate): src/graphcuda/cuda/gcn.cu:27-52."""
+    _check_layer_args(X, adj, W)
+    _require(dY.is_cuda and dY.dtype == torch.float32, "Y_grad must be a float32 CUDA tensor")
+    G = ops.mask_mul(dY, mask) if relu else (dY if dY.stride(1) == 1 else dY.contiguous())
+    AX = _adj_matmul(adj, X, precision)
+    dW = ops.gemm(AX.t(), G, precision=precision)
+    T = ops.gemm(G, W.t(), precision=precision)
+    dX = _adj_matmul(adj, T, precision)
+    return dX, dW

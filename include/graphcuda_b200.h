@@ -1,0 +1,185 @@
+/*
+ * graphcuda_b200 -- C ABI of the B200 (sm_100a) GCN layer engine.
+ *
+ * Every entry point takes plain device pointers, 64-bit sizes / leading
+ * dimensions (in elements) and the CUDA stream to enqueue on (a cudaStream_t
+ * passed as void*).  Entry points enqueue work and return; they never
+ * allocate device memory, never synchronise the device and never throw.
+ * Callers own every buffer, including the scratch ("workspace") buffers whose
+ * sizes the *_bytes queries report.  Return value: GC_OK (0) or a negative
+ * GC_ERR_* code; gc_last_error() gives a thread-local message for the last
+ * failure on the calling thread.
+ *
+ * All matrices are row-major fp32.  "ld" is the distance in elements between
+ * consecutive rows.
+ *
+ * Each declaration cites the reference interface (path within the GraphCUDA
+ * project : lines) whose work it takes over.
+ */
+#ifndef GRAPHCUDA_B200_H
+#define GRAPHCUDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GC_OK 0
+#define GC_ERR_INVALID (-1)      /* bad argument (null pointer, negative size, misaligned, overflow) */
+#define GC_ERR_UNSUPPORTED (-2)  /* valid request this build cannot serve (e.g. tensor-core path on an odd ld) */
+#define GC_ERR_CUDA (-3)         /* a CUDA runtime / driver call or kernel launch failed */
+#define GC_ERR_WORKSPACE (-4)    /* workspace pointer null or too small */
+#define GC_ERR_DEVICE_FLAG (-5)  /* a kernel reported a bounded wait that ran out (read back by gc_gemm_check_flag) */
+
+/* ---- library ---------------------------------------------------------- */
+
+/* ABI version, bumped when a signature changes. */
+int gc_abi_version(void);
+/* Message for the last failure on this thread ("" if none). */
+const char* gc_last_error(void);
+/* Static text for a GC_* code. */
+const char* gc_status_string(int status);
+
+/* ---- CSR sparse x dense (aggregation) ---------------------------------- */
+
+/*
+ * Replaces: src/graphcuda/cuda/spmm_cusparse.cu:3-126 (cusparseSpMM on a COO
+ * adjacency) as used by gcn_conv_forward / gcn_conv_backward
+ * (src/graphcuda/cuda/gcn.cu:12,40,49).
+ *
+ * A "plan" is derived once per CSR structure: the list of long rows (more
+ * than GC_SPMM_LONG_ROW non-zeros) and their split into fixed-size segments,
+ * so that heavy-tailed degree distributions do not serialise on one warp.
+ * The plan lives in caller memory of gc_spmm_plan_bytes(M) bytes and only
+ * depends on rowptr.
+ */
+#define GC_SPMM_LONG_ROW 1024 /* rows with more non-zeros than this take the segmented path */
+#define GC_SPMM_SEGMENT 2048  /* non-zeros per segment of a long row */
+
+size_t gc_spmm_plan_bytes(int64_t M);
+/* Builds the plan on `stream`.  plan must be 16-byte aligned device memory. */
+int gc_spmm_plan_build(const int32_t* rowptr, int64_t M, void* plan, size_t plan_bytes, void* stream);
+/* Upper bound of the scratch gc_spmm_csr_f32 needs for a structure with nnz
+ * non-zeros and F feature columns (partial sums of long-row segments). */
+size_t gc_spmm_scratch_bytes(int64_t nnz, int64_t F);
+
+#define GC_EPI_RELU 1        /* out = max(out, 0) computed as out * (out > 0), reference gcn.cu:19-20 */
+#define GC_EPI_ACCUMULATE 2  /* out += result instead of out = result (bias/relu applied after the add) */
+
+/*
+ * Y[M,F] = A_csr[M,K] * H[K,F] (+ bias[F]) (ReLU).  mask, when non-null,
+ * receives (pre-activation > 0) as 0.0f/1.0f with leading dimension ldY
+ * (the fp32 mask of reference gcn.cu:19).  plan may be null: then every row
+ * takes the row-per-warp path.  scratch may be null only when plan is null.
+ * No atomics: results are deterministic run to run.
+ */
+int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
+                    int64_t M, int64_t K, int64_t F,
+                    const float* H, int64_t ldH,
+                    const float* bias, int epilogue,
+                    float* Y, int64_t ldY, float* mask,
+                    const void* plan, void* scratch, size_t scratch_bytes,
+                    void* stream);
+
+/* ---- dense GEMM --------------------------------------------------------- */
+
+/*
+ * Replaces: gemm_cublas (src/graphcuda/cuda/gemm_cublas.cu:3-55) and the four
+ * hand-written SGEMMs matmul1..4 (src/graphcuda/cuda/matmul1.cu:27-61,
+ * matmul2.cu:65-100, matmul3.cu:194-243, matmul4.cu:209-265); also the
+ * transpose copies the reference makes before its backward GEMMs
+ * (gemm_cublas.cu:11-16 called from gcn.cu:43,46): op(A)/op(B) are read in
+ * place.
+ *
+ * C[M,N] = op(A)[M,K] * op(B)[K,N] (+ bias[N]) (ReLU), optional fp32 mask as
+ * above (leading dimension ldc).  transA=0: A is stored M x K; transA=1: A is
+ * stored K x M.  transB likewise (transB=0: K x N; transB=1: N x K).
+ */
+#define GC_PREC_AUTO (-1)      /* fp32 semantics: TF32X3 on tensor cores when the shape qualifies, else FP32_SIMT */
+#define GC_PREC_FP32_SIMT 0    /* IEEE fp32 FMA on CUDA cores, fixed summation order */
+#define GC_PREC_TF32X3 1       /* tcgen05 kind::tf32, split operands, three MMA passes, fp32 accumulate in TMEM */
+#define GC_PREC_TF32 2         /* tcgen05 kind::tf32, one pass (opt-in, 1e-2 tolerance tier) */
+
+#define GC_EPI_TRANSPOSED_OUT 4 /* store C transposed: C is N x M with leading dimension ldc (mask likewise) */
+
+size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int64_t K, int precision);
+int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K,
+                const float* A, int64_t lda, const float* B, int64_t ldb,
+                float* C, int64_t ldc,
+                const float* bias, int epilogue, float* mask,
+                int precision, void* workspace, size_t workspace_bytes,
+                void* stream);
+/* Which path gc_gemm_f32 would take for these arguments: one of GC_PREC_*
+ * (never AUTO), or a negative error. */
+int gc_gemm_resolve_precision(int transA, int transB, int64_t M, int64_t N, int64_t K,
+                              int64_t lda, int64_t ldb, int64_t ldc, int precision);
+/* Tensor-core kernels bound every wait; a wait that ran out sets a flag word
+ * at the start of the workspace.  Synchronises `stream`, reads it back and
+ * returns GC_OK or GC_ERR_DEVICE_FLAG (debug / test use). */
+int gc_gemm_check_flag(const void* workspace, void* stream);
+
+/* ---- ReLU mask helpers (reference gcn.cu:19-20,36) ----------------------- */
+
+/* G = dY * (Y > 0), element-wise over an M x N view (reference gcn.cu:36 with
+ * the mask re-derived from the saved activation instead of a stored fp32 mask). */
+int gc_relu_backward_f32(const float* dY, int64_t lddy, const float* Y, int64_t ldy,
+                         float* G, int64_t ldg, int64_t M, int64_t N, void* stream);
+/* G = dY * mask for a stored fp32 mask (reference gcn.cu:36 verbatim). */
+int gc_mask_mul_f32(const float* dY, int64_t lddy, const float* mask, int64_t ldm,
+                    float* G, int64_t ldg, int64_t M, int64_t N, void* stream);
+/* out = in^T : in is M x N (ldin), out is N x M (ldout). */
+int gc_transpose_f32(const float* in, int64_t ldin, float* out, int64_t ldout,
+                     int64_t M, int64_t N, void* stream);
+
+/* ---- adjacency construction (reference tests/gcn/graphcuda_impl.py:27-38) - */
+
+/*
+ * Row pointer of a coalesced COO matrix: rows[nnz] sorted ascending (int64, as
+ * torch's coalesce() leaves them; spmm_cusparse.cu:18,33-41) -> rowptr[M+1].
+ */
+int gc_coo_rows_to_rowptr(const int64_t* rows, int64_t nnz, int64_t M, int32_t* rowptr, void* stream);
+/* int64 -> int32 narrowing of column indices. */
+int gc_narrow_i64_i32(const int64_t* src, int32_t* dst, int64_t n, void* stream);
+
+/*
+ * Symmetric GCN normalisation of an edge list that already contains the
+ * self-loops: deg[i] = number of edges whose *target* (col) is i, weights
+ * w_e = deg[row]^-1/2 * deg[col]^-1/2 with IEEE-rounded 1/sqrt and products
+ * (bit-identical to torch CPU pow(-0.5) and left-to-right multiplication),
+ * inf -> 0 for isolated nodes.  Takes over torch_geometric's gcn_norm as
+ * called at tests/gcn/graphcuda_impl.py:28.
+ *   deg_scratch: N floats.  w: E floats out.
+ */
+int gc_gcn_norm_f32(const int64_t* row, const int64_t* col, int64_t E, int64_t N,
+                    float* deg_scratch, float* w, void* stream);
+
+/*
+ * CSR from an edge list sorted by (row, col) with duplicates allowed:
+ * duplicates are summed in input order (what coalesce() does,
+ * tests/gcn/graphcuda_impl.py:33-38).  Two steps so the caller can size the
+ * outputs: gc_csr_count_unique writes the number of distinct (row,col) pairs
+ * to *nnz_out (device int64) and a head flag per edge into head[E] (int32
+ * scratch holding the exclusive running count afterwards); gc_csr_fill then
+ * writes rowptr[M+1], col[nnz], val[nnz].
+ */
+size_t gc_csr_build_workspace_bytes(int64_t E);
+int gc_csr_count_unique(const int64_t* row, const int64_t* col, int64_t E,
+                        int32_t* head, int64_t* nnz_out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int gc_csr_fill(const int64_t* row, const int64_t* col, const float* w, int64_t E, int64_t M,
+                const int32_t* head, int32_t* rowptr, int32_t* csr_col, float* csr_val,
+                void* stream);
+
+/* 1 written to *out (device int32) when the CSR matrix with sorted columns
+ * equals its transpose bit for bit, else 0.  Decides whether the engine may
+ * aggregate on the output side (the reference multiplies by A, never A^T:
+ * gcn.cu:49). */
+int gc_csr_is_symmetric(const int32_t* rowptr, const int32_t* col, const float* val,
+                        int64_t M, int32_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRAPHCUDA_B200_H */

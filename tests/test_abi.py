@@ -1,0 +1,86 @@
+"""The C-ABI library loads and exports every symbol the header declares, the
+ctypes table mirrors the header, and argument validation answers without
+touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from graphcuda_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "graphcuda_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_is_built():
+    assert os.path.exists(build.lib_path()), "run python -m graphcuda_b200.build"
+
+
+def test_every_declared_symbol_is_exported():
+    handle = ctypes.CDLL(build.lib_path())
+    names = declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(handle, n), f"{n} declared in the header but not exported"
+
+
+def test_ctypes_table_matches_header():
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_header_cites_the_reference():
+    text = open(HEADER).read()
+    for needle in ("spmm_cusparse.cu", "gemm_cublas.cu", "matmul1.cu", "gcn.cu", "graphcuda_impl.py"):
+        assert needle in text
+
+
+def test_status_strings_and_version():
+    L = _lib.lib()
+    assert L.gc_abi_version() >= 1
+    assert L.gc_status_string(0) == b"ok"
+    assert b"workspace" in L.gc_status_string(-4)
+
+
+def test_argument_validation_without_gpu():
+    L = _lib.lib()
+    # negative size
+    assert L.gc_gemm_f32(0, 0, -1, 4, 4, None, 4, None, 4, None, 4, None, 0, None, 0, None, 0, None) == -1
+    assert b"negative" in L.gc_last_error()
+    # leading dimension too small
+    assert L.gc_gemm_f32(0, 0, 8, 8, 8, 16, 4, 16, 8, 16, 8, None, 0, None, 0, None, 0, None) == -1
+    # unknown epilogue bit
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, None, 0, None) == -1
+    # empty problems succeed without launching anything
+    assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, 0, None, 0, None) == 0
+    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, None) == 0
+    with pytest.raises(RuntimeError):
+        _lib.check(-1, "probe")
+
+
+def test_plan_and_workspace_sizes():
+    L = _lib.lib()
+    assert L.gc_spmm_plan_bytes(0) >= 16
+    assert L.gc_spmm_plan_bytes(1000) >= 16 + 4 * 1000 + 4 * 1001
+    assert L.gc_spmm_scratch_bytes(10_000_000, 256) >= (10_000_000 // 1024) * 256 * 4
+    assert L.gc_gemm_workspace_bytes(0, 0, 4096, 256, 256, _lib.PREC_TF32X3) >= 256 + 2 * 256 * 256 * 4
+
+
+def test_precision_resolution_is_host_logic():
+    L = _lib.lib()
+    P = _lib
+    # small problem -> CUDA cores; large aligned problem -> split-TF32 tensor cores
+    assert L.gc_gemm_resolve_precision(0, 0, 2708, 16, 1433, 1433, 16, 16, P.PREC_AUTO) == P.PREC_FP32_SIMT
+    assert L.gc_gemm_resolve_precision(0, 0, 169343, 256, 128, 128, 256, 256, P.PREC_AUTO) == P.PREC_TF32X3
+    # unaligned row pitch of an operand read in place -> CUDA cores under AUTO, error when forced
+    assert L.gc_gemm_resolve_precision(0, 0, 169343, 256, 127, 127, 256, 256, P.PREC_AUTO) == P.PREC_FP32_SIMT
+    assert L.gc_gemm_resolve_precision(0, 0, 169343, 256, 127, 127, 256, 256, P.PREC_TF32) == -2
+    # weight-gradient shape (few tiles, huge K) stays on the split-K CUDA-core kernel
+    assert L.gc_gemm_resolve_precision(1, 0, 256, 256, 2449029, 256, 256, 256, P.PREC_AUTO) == P.PREC_FP32_SIMT
+    assert L.gc_gemm_resolve_precision(0, 0, 8192, 8192, 8192, 8192, 8192, 8192, P.PREC_FP32_SIMT) == P.PREC_FP32_SIMT
