@@ -5,9 +5,14 @@ operator functions ``matmul1..4``, ``gemm_cublas``, ``spmm_cusparse``.
 Importing the package needs the built C-ABI library
 (``python -m graphcuda_b200.build``); there is no fallback path.
 """
+import sys as _sys
+
 from . import _lib
 
-_lib.lib()  # fail loudly at import when the CUDA library is missing
+# Fail loudly at import when the CUDA library is missing or stale -- except
+# while `python -m graphcuda_b200.build` is (re)building it.
+if "graphcuda_b200.build" not in getattr(_sys, "orig_argv", []):
+    _lib.lib()
 
 from . import _graphcuda  # noqa: E402
 from ._graphcuda import (gemm_cublas, matmul1, matmul2, matmul3, matmul4,  # noqa: E402

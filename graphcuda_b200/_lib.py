@@ -22,6 +22,7 @@ _size = C.c_size_t
 # name -> (restype, argtypes); mirrors include/graphcuda_b200.h one to one
 SIGNATURES = {
     "gc_abi_version": (_int, []),
+    "gc_launch_count": (C.c_longlong, []),
     "gc_last_error": (C.c_char_p, []),
     "gc_status_string": (C.c_char_p, [_int]),
     "gc_spmm_plan_bytes": (_size, [_i64]),

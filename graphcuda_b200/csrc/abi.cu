@@ -1,13 +1,20 @@
 // Library-level entry points: version, status text, thread-local error text.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstring>
 
 namespace {
 thread_local char g_last_error[512] = {0};
 }
 
+namespace {
+std::atomic<long long> g_launches{0};
+}
+
 namespace gc {
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
 int fail(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -20,6 +27,8 @@ int fail(int code, const char* fmt, ...) {
 extern "C" {
 
 int gc_abi_version(void) { return 1; }
+
+long long gc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* gc_last_error(void) { return g_last_error; }
 

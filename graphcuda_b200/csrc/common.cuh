@@ -16,7 +16,11 @@ int fail(int code, const char* fmt, ...);
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
-inline int check_launch(const char* what) {
+// Process-wide count of kernel launches issued by this library (gc_launch_count()).
+void count_launches(int n);
+
+inline int check_launch(const char* what, int launches = 1) {
+  count_launches(launches);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   return GC_OK;

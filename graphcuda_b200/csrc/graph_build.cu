@@ -168,7 +168,7 @@ int gc_gcn_norm_f32(const int64_t* row, const int64_t* col, int64_t E, int64_t N
   degree_kernel<<<grid_for(E), 256, 0, st>>>(col, E, deg);
   dinv_kernel<<<grid_for(N), 256, 0, st>>>(deg, N);
   norm_weight_kernel<<<grid_for(E), 256, 0, st>>>(row, col, E, deg_scratch, w);
-  return gc::check_launch("gc_gcn_norm_f32");
+  return gc::check_launch("gc_gcn_norm_f32", 3);
 }
 
 size_t gc_csr_build_workspace_bytes(int64_t E) {
@@ -194,7 +194,7 @@ int gc_csr_count_unique(const int64_t* row, const int64_t* col, int64_t E, int32
     if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "gc_csr_count_unique: scan: %s", cudaGetErrorString(e));
   }
   total_kernel<<<1, 1, 0, st>>>(row, col, E, head, nnz_out);
-  return gc::check_launch("gc_csr_count_unique");
+  return gc::check_launch("gc_csr_count_unique", E > 0 ? 2 : 1);
 }
 
 int gc_csr_fill(const int64_t* row, const int64_t* col, const float* w, int64_t E, int64_t M, const int32_t* head,
@@ -218,7 +218,7 @@ int gc_csr_is_symmetric(const int32_t* rowptr, const int32_t* col, const float* 
     const unsigned grid = unsigned(std::min<int64_t>(gc::ceil_div(M, 8), gc::kNumSMs * 16));
     symmetric_kernel<<<grid, 256, 0, st>>>(rowptr, col, val, int(M), out);
   }
-  return gc::check_launch("gc_csr_is_symmetric");
+  return gc::check_launch("gc_csr_is_symmetric", M > 0 ? 2 : 1);
 }
 
 }  // extern "C"

@@ -424,7 +424,7 @@ int gc_spmm_plan_build(const int32_t* rowptr, int64_t M, void* plan, size_t plan
   auto* seg_off = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_seg_off_offset(M));
   if (M > 0) plan_collect_kernel<<<unsigned((M + 255) / 256), 256, 0, st>>>(rowptr, int(M), hdr, seg_off);
   plan_scan_kernel<<<1, 1024, 0, st>>>(rowptr, int(M), hdr, long_rows, seg_off);
-  return gc::check_launch("gc_spmm_plan_build");
+  return gc::check_launch("gc_spmm_plan_build", M > 0 ? 2 : 1);
 }
 
 size_t gc_spmm_scratch_bytes(int64_t nnz, int64_t F) {

@@ -1,0 +1,23 @@
+"""The stacked model of the reference's training script
+(tests/gcn/graphcuda_impl.py:15-24), generalised to any depth: GCNConv layers
+with ReLU on all but the last, ``log_softmax`` on top."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .gcn import GCNConv
+
+
+class GCN(torch.nn.Module):
+    def __init__(self, dims: Sequence[int], *, precision: Optional[str] = None):
+        super().__init__()
+        self.convs = torch.nn.ModuleList(
+            [GCNConv(dims[i], dims[i + 1], apply_relu=(i < len(dims) - 2), precision=precision)
+             for i in range(len(dims) - 1)])
+
+    def forward(self, x, adj):
+        for conv in self.convs:
+            x = conv(x, adj)
+        return torch.log_softmax(x, dim=1)

@@ -1,0 +1,253 @@
+"""Row-partitioned GCN layer for graphs spread over several GPUs (one process
+per GPU, ``torch.distributed``; NCCL over NVLink on the GPUs, gloo in the CPU
+tests).  The reference has no distributed code; this extends its layer
+(src/graphcuda/cuda/gcn.cu:5-52) to the 1-D row partition:
+
+  * rank r owns rows [r*B, (r+1)*B) of the normalised adjacency (all columns,
+    global column ids), the matching rows of every feature matrix, and a
+    replica of every weight;
+  * the one exchange per aggregation is an all-gather of the row blocks of
+    the matrix being aggregated (X, H = X W, or the backward counterparts);
+  * the local rows' adjacency is split by column into the diagonal block
+    (columns owned by this rank) and the rest, so the diagonal-block SpMM runs
+    on the compute stream while the all-gather is in flight, and the
+    off-diagonal SpMM accumulates on top once the gathered matrix has landed
+    in local memory (remote rows are never read through peer pointers);
+  * weight gradients are summed with an all-reduce (tiny: in x out).
+
+The numerical work goes through a small backend object so that the same
+orchestration runs on CUDA (this library's kernels) and, in the CPU tests,
+on torch CPU ops under gloo.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------- partition arithmetic
+class RowPartition:
+    """Uniform contiguous row blocks of size ceil(n / world); the last block may
+    be short (or empty)."""
+
+    def __init__(self, n: int, world: int):
+        if n < 0 or world < 1:
+            raise ValueError("RowPartition: n >= 0 and world >= 1 required")
+        self.n = n
+        self.world = world
+        self.block = -(-n // world) if n else 0
+        self.padded = self.block * world
+
+    def bounds(self, rank: int):
+        if not 0 <= rank < self.world:
+            raise ValueError("rank out of range")
+        lo = min(rank * self.block, self.n)
+        hi = min(lo + self.block, self.n)
+        return lo, hi
+
+    def owner(self, row: int) -> int:
+        return row // self.block if self.block else 0
+
+
+def slice_csr_rows(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, lo: int, hi: int):
+    """Rows [lo, hi) of a CSR matrix as a CSR matrix (column ids untouched)."""
+    s = int(rowptr[lo])
+    e = int(rowptr[hi])
+    rp = (rowptr[lo:hi + 1] - rowptr[lo]).to(rowptr.dtype)
+    return rp, col[s:e], val[s:e]
+
+
+def split_csr_columns(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, lo: int, hi: int):
+    """Splits a CSR matrix into the entries with lo <= col < hi (column ids
+    rebased to col - lo) and the rest (column ids untouched).  Order within a
+    row is preserved in both parts."""
+    inside = (col >= lo) & (col < hi)
+    csum = torch.zeros(col.numel() + 1, dtype=torch.int64, device=col.device)
+    torch.cumsum(inside.to(torch.int64), 0, out=csum[1:])
+    rp64 = rowptr.to(torch.int64)
+    rp_in = csum[rp64]
+    rp_out = rp64 - rp_in
+    part_in = (rp_in.to(rowptr.dtype), (col[inside] - lo).to(col.dtype), val[inside])
+    part_out = (rp_out.to(rowptr.dtype), col[~inside], val[~inside])
+    return part_in, part_out
+
+
+# ---------------------------------------------------------------- backends
+class CudaBackend:
+    """This library's kernels."""
+
+    def make_adj(self, rowptr, col, val, shape):
+        from .adjacency import CSRAdjacency
+        return CSRAdjacency(rowptr.contiguous(), col.contiguous(), val.contiguous(), shape, symmetric=False)
+
+    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None):
+        return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into)
+
+    def gemm(self, A, B, *, bias=None, relu=False, precision=None):
+        from . import ops
+        return ops.gemm(A, B, bias=bias, relu=relu, precision=precision)
+
+    def relu_backward(self, dY, Y):
+        from . import ops
+        return ops.relu_backward(dY, Y)
+
+
+# ---------------------------------------------------------------- partitioned graph
+class PartitionedGraph:
+    """This rank's rows of a (symmetric) normalised adjacency, split into the
+    diagonal block and the remainder, plus the gather buffers."""
+
+    def __init__(self, rowptr, col, val, n_nodes: int, *, rank: Optional[int] = None,
+                 world: Optional[int] = None, group=None, backend=None, rows_are_local: bool = False):
+        """rowptr/col/val: the GLOBAL CSR (every rank passes the same), or with
+        rows_are_local=True this rank's row block only (global column ids)."""
+        self.group = group
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.world = dist.get_world_size(group) if world is None else world
+        self.part = RowPartition(n_nodes, self.world)
+        self.lo, self.hi = self.part.bounds(self.rank)
+        self.n = n_nodes
+        self.rows = self.hi - self.lo
+        self.backend = backend or CudaBackend()
+        if not rows_are_local:
+            rowptr, col, val = slice_csr_rows(rowptr, col, val, self.lo, self.hi)
+        self.nnz_local_rows = int(col.numel())
+        (rp_d, c_d, v_d), (rp_o, c_o, v_o) = split_csr_columns(rowptr, col, val, self.lo, self.hi)
+        self.diag = self.backend.make_adj(rp_d, c_d, v_d, (self.rows, max(self.rows, 0)))
+        self.offd = self.backend.make_adj(rp_o, c_o, v_o, (self.rows, self.part.padded))
+        self.nnz_diag = int(c_d.numel())
+        self.nnz_offd = int(c_o.numel())
+        self.device = val.device
+        self._gather_bufs = {}
+        self._stage_bufs = {}
+
+    # -- collectives ----------------------------------------------------------
+    def _gather_buffer(self, F: int, tag: str):
+        key = (F, tag)
+        buf = self._gather_bufs.get(key)
+        if buf is None:
+            buf = torch.zeros((self.part.padded, F), dtype=torch.float32, device=self.device)
+            self._gather_bufs[key] = buf
+        return buf
+
+    def all_gather_rows_async(self, H_local: torch.Tensor, tag: str = "a"):
+        """Starts the all-gather of the row blocks; returns (gathered, work).
+        `gathered` is indexable by global row id once work.wait() returned."""
+        F = H_local.size(1)
+        out = self._gather_buffer(F, tag)
+        src = H_local
+        if self.rows != self.part.block or not H_local.is_contiguous():
+            key = (F, tag)
+            st = self._stage_bufs.get(key)
+            if st is None:
+                st = torch.zeros((self.part.block, F), dtype=torch.float32, device=self.device)
+                self._stage_bufs[key] = st
+            st[:self.rows].copy_(H_local)
+            src = st
+        if self.world == 1:
+            out[:self.part.block].copy_(src)
+            return out, None
+        work = dist.all_gather_into_tensor(out, src, group=self.group, async_op=True)
+        return out, work
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    # -- aggregation ----------------------------------------------------------
+    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a"):
+        """rows_r of A @ H for H given by its local row block: diagonal block
+        first (overlapping the all-gather), then the off-diagonal remainder with
+        the fused bias/ReLU.  `gathered` short-circuits the exchange when the
+        full matrix is already resident (constant input features)."""
+        work = None
+        if gathered is None:
+            gathered, work = self.all_gather_rows_async(H_local, tag)
+        Y = self.backend.spmm(self.diag, H_local)
+        if work is not None:
+            work.wait()
+        return self.backend.spmm(self.offd, gathered, bias=bias, relu=relu, accumulate_into=Y)
+
+
+class DistGCNConvFunction(torch.autograd.Function):
+    """One layer on the local row block; collectives inside forward/backward.
+    The returned weight gradient is already summed over ranks."""
+
+    @staticmethod
+    def forward(ctx, X, graph: PartitionedGraph, W, apply_relu, bias, precision, X_gathered):
+        be = graph.backend
+        fin, fout = W.shape
+        transform_first = fout < fin  # the partitioned adjacency is symmetric by contract
+        if transform_first:
+            H = be.gemm(X, W, precision=precision)
+            Y = graph.aggregate(H, bias=bias, relu=bool(apply_relu), tag="f")
+            inter = None
+        else:
+            AX = graph.aggregate(X, gathered=X_gathered, tag="f")
+            Y = be.gemm(AX, W, bias=bias, relu=bool(apply_relu), precision=precision)
+            inter = AX
+        ctx.graph = graph
+        ctx.transform_first = transform_first
+        ctx.apply_relu = bool(apply_relu)
+        ctx.precision = precision
+        ctx.has_bias = bias is not None
+        ctx.has_inter = inter is not None
+        ctx.save_for_backward(*([X, W, Y] + ([inter] if inter is not None else [])))
+        return Y
+
+    @staticmethod
+    def backward(ctx, dY):
+        graph = ctx.graph
+        be = graph.backend
+        saved = ctx.saved_tensors
+        X, W, Y = saved[:3]
+        need_dX = ctx.needs_input_grad[0]
+        need_dW = ctx.needs_input_grad[2]
+        dY = dY.contiguous()
+        G = be.relu_backward(dY, Y) if ctx.apply_relu else dY
+        dX = dW = db = None
+        if ctx.has_bias and ctx.needs_input_grad[4]:
+            db = graph.all_reduce_sum(G.sum(0))
+        if ctx.transform_first:
+            S = graph.aggregate(G, tag="b")  # A^T G = A G (symmetric)
+            if need_dW:
+                dW = graph.all_reduce_sum(be.gemm(X.t(), S, precision=ctx.precision))
+            if need_dX:
+                dX = be.gemm(S, W.t(), precision=ctx.precision)
+        else:
+            AX = saved[3]
+            if need_dW:
+                dW = graph.all_reduce_sum(be.gemm(AX.t(), G, precision=ctx.precision))
+            if need_dX:
+                T = be.gemm(G, W.t(), precision=ctx.precision)
+                dX = graph.aggregate(T, tag="b")
+        return dX, None, dW, None, db, None, None
+
+
+class DistGCN(torch.nn.Module):
+    """Stack of layers as in the reference's training script
+    (tests/gcn/graphcuda_impl.py:15-24) over a PartitionedGraph: ReLU on all
+    layers but the last, log_softmax on top.  Every rank must construct it with
+    the same RNG state so the weight replicas agree."""
+
+    def __init__(self, dims, *, precision: Optional[str] = None):
+        super().__init__()
+        import math
+        self.precision = precision
+        self.weights = torch.nn.ParameterList()
+        for i in range(len(dims) - 1):
+            s = math.sqrt(2.0 / (dims[i] + dims[i + 1]))
+            w = torch.Tensor(dims[i], dims[i + 1])
+            w.uniform_(-s, s)  # same initialiser as src/graphcuda/python/gcn.py:43-45
+            self.weights.append(torch.nn.Parameter(w))
+
+    def forward(self, X_local, graph: PartitionedGraph, X_gathered=None):
+        h = X_local
+        last = len(self.weights) - 1
+        for i, W in enumerate(self.weights):
+            h = DistGCNConvFunction.apply(h, graph, W, i < last, None, self.precision,
+                                          X_gathered if i == 0 else None)
+        return torch.log_softmax(h, dim=1)

@@ -37,6 +37,8 @@ extern "C" {
 
 /* ABI version, bumped when a signature changes. */
 int gc_abi_version(void);
+/* Kernels this library has launched in this process so far (all threads). */
+long long gc_launch_count(void);
 /* Message for the last failure on this thread ("" if none). */
 const char* gc_last_error(void);
 /* Static text for a GC_* code. */

@@ -1,0 +1,251 @@
+"""GCNConv forward/backward vs the oracle (the reference's ATen composition,
+src/graphcuda/cpp/gcn.cpp, on CPU) and vs the fixtures its code produced."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gcn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4
+TOL_TF32 = 1e-2
+
+
+def _t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def _graph(n, avg_deg, seed):
+    from graphcuda_b200 import synth
+    scale = max(4, (n - 1).bit_length())
+    e = synth.rmat_edges(scale, n, int(n * avg_deg / 2), seed)
+    return O.normalized_adjacency_coo(synth.symmetrize(e), n)
+
+
+def _adj_variant(A, kind, dev):
+    if kind == "dense":
+        return A.to_dense().to(dev)
+    if kind == "coo":
+        return A.to(dev)
+    if kind == "csr":
+        return A.to_sparse_csr().to(dev)
+    rowptr, col, val = O.coo_to_csr_int32(A)
+    return (rowptr.to(dev), col.to(dev), val.to(dev))
+
+
+@pytest.mark.parametrize("kind", ["dense", "coo", "csr", "tuple"])
+@pytest.mark.parametrize("dims", [(40, 12), (12, 40), (33, 33), (100, 7)])
+@pytest.mark.parametrize("relu", [True, False])
+def test_layer_forward_backward(cuda, kind, dims, relu):
+    """Both aggregation orders (in <= out and out < in), all adjacency layouts."""
+    import graphcuda
+    fin, fout = dims
+    n = 600
+    A = _graph(n, 8, seed=fin)
+    g = torch.Generator().manual_seed(fin * 100 + fout)
+    X = torch.randn(n, fin, generator=g)
+    dY = torch.randn(n, fout, generator=g)
+    torch.manual_seed(3)
+    conv = graphcuda.GCNConv(fin, fout, apply_relu=relu)
+    torch.manual_seed(3)
+    ref = O.GCNConv(fin, fout, apply_relu=relu)
+    assert torch.equal(conv.weights.detach(), ref.weights.detach())  # same initialiser, same RNG use
+    assert list(conv.state_dict().keys()) == ["weights"]
+    conv = conv.to(cuda)
+
+    Xr = X.clone().requires_grad_()
+    Yr = ref(Xr, A)
+    Yr.backward(dY)
+    Xg = X.to(cuda).requires_grad_()
+    Y = conv(Xg, _adj_variant(A, kind, cuda))
+    Y.backward(dY.to(cuda))
+    assert O.rel_fro(Y, Yr) < TOL and O.rel_max(Y, Yr) < TOL * 10
+    assert O.rel_fro(Xg.grad, Xr.grad) < TOL
+    assert O.rel_fro(conv.weights.grad, ref.weights.grad) < TOL
+
+
+def test_extension_level_functions(cuda):
+    """graphcuda._graphcuda.gcn_conv_forward / gcn_conv_backward keep the
+    reference's signatures and return conventions (gcn.cuh:6-18)."""
+    import graphcuda
+    n, fin, fout = 500, 24, 16
+    A = _graph(n, 6, seed=1)
+    g = torch.Generator().manual_seed(0)
+    X, W, dY = torch.randn(n, fin, generator=g), torch.randn(fin, fout, generator=g), torch.randn(n, fout, generator=g)
+    Yr, mr = O.gcn_conv_forward(X, A, W, True)
+    dXr, dWr = O.gcn_conv_backward(dY, X, A, W, True, mr)
+    Ag = A.to(cuda)
+    Y, m = graphcuda._graphcuda.gcn_conv_forward(X.to(cuda), Ag, W.to(cuda), True)
+    assert m.shape == (n, fout) and m.dtype == torch.float32 and m.is_cuda
+    assert O.rel_fro(Y, Yr) < TOL
+    dX, dW = graphcuda._graphcuda.gcn_conv_backward(dY.to(cuda), X.to(cuda), Ag, W.to(cuda), True, m)
+    assert O.rel_fro(dX, dXr) < TOL and O.rel_fro(dW, dWr) < TOL
+    Y0, m0 = graphcuda._graphcuda.gcn_conv_forward(X.to(cuda), Ag, W.to(cuda), False)
+    assert m0.dim() == 0 and not m0.is_cuda  # 0-dim CPU tensor, gcn.cu:22
+    dX0, dW0 = graphcuda._graphcuda.gcn_conv_backward(dY.to(cuda), X.to(cuda), Ag, W.to(cuda), False, m0)
+    dXr0, dWr0 = O.gcn_conv_backward(dY, X, A, W, False, torch.empty(()))
+    assert O.rel_fro(dX0, dXr0) < TOL and O.rel_fro(dW0, dWr0) < TOL
+    with pytest.raises(RuntimeError):
+        graphcuda._graphcuda.gcn_conv_forward(X, A, W, True)  # CPU tensors: no CPU path
+
+
+def test_non_symmetric_adjacency_follows_the_reference(cuda):
+    """The reference multiplies by A (not A^T) in the backward pass
+    (gcn.cu:49); for a non-symmetric A that is what must come out."""
+    import graphcuda
+    from tests.helpers import random_csr
+    n, fin, fout = 300, 30, 10  # out < in: would pick transform-first if A were symmetric
+    A = random_csr(n, n, 5.0, seed=4)
+    g = torch.Generator().manual_seed(1)
+    X, dY = torch.randn(n, fin, generator=g), torch.randn(n, fout, generator=g)
+    torch.manual_seed(5)
+    conv = graphcuda.GCNConv(fin, fout).to(cuda)
+    torch.manual_seed(5)
+    ref = O.GCNConv(fin, fout)
+    Xr = X.clone().requires_grad_()
+    ref(Xr, A).backward(dY)
+    Xg = X.to(cuda).requires_grad_()
+    conv(Xg, A.to(cuda)).backward(dY.to(cuda))
+    assert O.rel_fro(Xg.grad, Xr.grad) < TOL
+    assert O.rel_fro(conv.weights.grad, ref.weights.grad) < TOL
+
+
+def test_golden_layers(cuda, golden_dir):
+    import graphcuda
+    g = np.load(os.path.join(golden_dir, "layer_dense.npz"))
+    A, X, W, dY = (_t(g[k]).to(cuda) for k in ("A", "X", "W", "dY"))
+    Y, m = graphcuda._graphcuda.gcn_conv_forward(X, A, W, True)
+    dX, dW = graphcuda._graphcuda.gcn_conv_backward(dY, X, A, W, True, m)
+    for name, got in (("Y", Y), ("dX", dX), ("dW", dW)):
+        assert O.rel_fro(got, _t(g[name])) < TOL, name
+    s = np.load(os.path.join(golden_dir, "layer_sparse.npz"))
+    n = int(s["n"])
+    As = torch.sparse_coo_tensor(torch.stack([_t(s["rows"]), _t(s["cols"])]), _t(s["vals"]), (n, n)).coalesce().to(cuda)
+    X, W, dY = (_t(s[k]).to(cuda) for k in ("X", "W", "dY"))
+    Y1, m1 = graphcuda._graphcuda.gcn_conv_forward(X, As, W, True)
+    dX1, dW1 = graphcuda._graphcuda.gcn_conv_backward(dY, X, As, W, True, m1)
+    for name, got in (("Y1", Y1), ("dX1", dX1), ("dW1", dW1)):
+        assert O.rel_fro(got, _t(s[name])) < TOL, name
+
+
+def test_golden_module_training(cuda, golden_dir):
+    """5 Adam steps of the 2-layer model: losses, weights and argmax of the
+    reference module's run."""
+    import graphcuda
+    g = np.load(os.path.join(golden_dir, "module_train.npz"))
+    A, X, y = _t(g["A"]).to(cuda), _t(g["X"]).to(cuda), _t(g["y"]).to(cuda)
+    torch.manual_seed(int(g["seed"]))
+    c1 = graphcuda.GCNConv(X.size(1), g["W1_0"].shape[1], apply_relu=True)
+    c2 = graphcuda.GCNConv(g["W2_0"].shape[0], g["W2_0"].shape[1], apply_relu=False)
+    assert torch.equal(c1.weights.detach(), _t(g["W1_0"])) and torch.equal(c2.weights.detach(), _t(g["W2_0"]))
+    c1, c2 = c1.to(cuda), c2.to(cuda)
+    opt = torch.optim.Adam(list(c1.parameters()) + list(c2.parameters()), lr=0.01)
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        out = torch.log_softmax(c2(c1(X, A), A), dim=1)
+        loss = torch.nn.functional.nll_loss(out[:20], y[:20])
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert np.allclose(losses, g["losses"], rtol=1e-4)
+    assert O.rel_fro(c1.weights, _t(g["W1"])) < TOL and O.rel_fro(c2.weights, _t(g["W2"])) < TOL
+    with torch.no_grad():
+        logits = torch.log_softmax(c2(c1(X, A), A), dim=1)
+    assert O.rel_fro(logits, _t(g["logits"])) < TOL
+    assert torch.equal(logits.argmax(1).cpu(), _t(g["logits"]).argmax(1))
+
+
+@pytest.mark.parametrize("kind", ["dense", "coo"])
+def test_cora_like_training_logits_and_argmax(cuda, kind):
+    """2-layer GCN, N=2708, 1433 -> 16 -> 7, 20 Adam epochs on the synthetic
+    Cora-shaped input: logits within 1e-4 and identical argmax."""
+    import graphcuda
+    from graphcuda_b200 import synth
+    cfg = synth.CONFIGS["cora_like"]
+    n = cfg["nodes"]
+    e = synth.preferential_attachment_edges(n, cfg["edges"], cfg["seed"])
+    A = O.normalized_adjacency_coo(synth.symmetrize(e), n)
+    X = synth.bow_features(n, cfg["features"], 0.0127, seed=1)
+    y = synth.uniform_labels(n, cfg["classes"], seed=2)
+    train, _, _ = synth.planetoid_split(n)
+    torch.manual_seed(0)
+    ref = O.GCN([cfg["features"], cfg["hidden"], cfg["classes"]])
+    torch.manual_seed(0)
+    c1 = graphcuda.GCNConv(cfg["features"], cfg["hidden"], apply_relu=True)
+    c2 = graphcuda.GCNConv(cfg["hidden"], cfg["classes"], apply_relu=False)
+    c1, c2 = c1.to(cuda), c2.to(cuda)
+    Aref = A.to_dense() if kind == "dense" else A
+    Ag = Aref.to(cuda)
+    Xg, yg, tg = X.to(cuda), y.to(cuda), train.to(cuda)
+    opt_r = torch.optim.Adam(ref.parameters(), lr=0.01)
+    opt_g = torch.optim.Adam(list(c1.parameters()) + list(c2.parameters()), lr=0.01)
+    for _ in range(20):
+        opt_r.zero_grad()
+        lr_ = torch.nn.functional.nll_loss(ref(X, Aref)[train], y[train])
+        lr_.backward()
+        opt_r.step()
+        opt_g.zero_grad()
+        out = torch.log_softmax(c2(c1(Xg, Ag), Ag), dim=1)
+        lg = torch.nn.functional.nll_loss(out[tg], yg[tg])
+        lg.backward()
+        opt_g.step()
+    assert abs(lr_.item() - lg.item()) < 1e-4 * max(1.0, abs(lr_.item()))
+    with torch.no_grad():
+        logits_r = ref(X, Aref)
+        logits_g = torch.log_softmax(c2(c1(Xg, Ag), Ag), dim=1).cpu()
+    assert O.rel_fro(logits_g, logits_r) < TOL
+    # identical argmax; a disagreement is only tolerable on a numerical tie
+    pr, pg = logits_r.argmax(1), logits_g.argmax(1)
+    if not torch.equal(pr, pg):
+        bad = (pr != pg).nonzero().flatten()
+        top2 = logits_r[bad].double().topk(2, dim=1).values
+        assert float((top2[:, 0] - top2[:, 1]).max()) < 1e-6, "argmax differs away from ties"
+
+
+def test_bias_relu_layer_arxiv_like_shape(cuda):
+    """Single layer with bias + ReLU on a reduced R-MAT graph, 128 -> 256 (the
+    tensor-core path): relu((A X) W + b) against the oracle, fp32 and TF32."""
+    import graphcuda
+    from graphcuda_b200 import synth
+    n = 20_000
+    A = _graph(n, 14, seed=2)
+    X = synth.normal_features(n, 128, seed=5)
+    b = synth.normal_features(1, 256, seed=6)[0] * 0.1
+    dY = synth.normal_features(n, 256, seed=7)
+    torch.manual_seed(11)
+    conv = graphcuda.GCNConv(128, 256, apply_relu=True, bias=True)
+    W = conv.weights.detach().clone()
+    with torch.no_grad():
+        conv.bias.copy_(b)
+    conv = conv.to(cuda)
+    Xr = X.clone().requires_grad_()
+    Wr = W.clone().requires_grad_()
+    br = b.clone().requires_grad_()
+    pre = A.mm(Xr).mm(Wr) + br
+    Yr = pre * (pre > 0)
+    Yr.backward(dY)
+    for prec, tol in ((None, TOL), ("tf32", TOL_TF32)):
+        conv.precision = prec
+        conv.zero_grad()
+        Xg = X.to(cuda).requires_grad_()
+        Y = conv(Xg, A.to(cuda))
+        Y.backward(dY.to(cuda))
+        assert O.rel_fro(Y, Yr) < tol, prec
+        assert O.rel_fro(Xg.grad, Xr.grad) < tol, prec
+        assert O.rel_fro(conv.weights.grad, Wr.grad) < tol, prec
+        assert O.rel_fro(conv.bias.grad, br.grad) < tol, prec
+    from graphcuda_b200 import ops
+    ops.check_gemm_flag(cuda)
+
+
+def test_input_layer_skips_dx(cuda):
+    import graphcuda
+    A = _graph(400, 6, seed=9)
+    X = torch.randn(400, 20).to(cuda)  # requires_grad False
+    conv = graphcuda.GCNConv(20, 8).to(cuda)
+    conv(X, A.to(cuda)).sum().backward()
+    assert conv.weights.grad is not None and X.grad is None

@@ -1,0 +1,158 @@
+"""Dense GEMM back ends vs the oracle (A @ B on CPU), through the C ABI."""
+import pytest
+import torch
+
+from oracle import gcn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-4
+TOL_TF32 = 1e-2
+
+
+def _rand(m, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.rand(m, n, generator=g) * 2 - 1  # uniform(-1, 1)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (5, 7, 3), (64, 64, 64), (65, 63, 17), (130, 200, 33),
+                                   (2708, 16, 1433), (2708, 7, 16), (300, 47, 256), (257, 129, 1000)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_simt_all_layouts(cuda, shape, ta, tb):
+    from graphcuda_b200 import gemm
+    M, N, K = shape
+    A = _rand(M, K, 1)
+    B = _rand(K, N, 2)
+    ref = O.matmul(A, B)
+    Ag = (A.t().contiguous().to(cuda).t() if ta else A.to(cuda))
+    Bg = (B.t().contiguous().to(cuda).t() if tb else B.to(cuda))
+    out = gemm(Ag, Bg, precision="fp32_simt")
+    assert out.shape == (M, N)
+    assert O.rel_fro(out, ref) < TOL_FP32 and O.rel_max(out, ref) < TOL_FP32
+
+
+def test_simt_split_k_weight_gradient_shape(cuda):
+    from graphcuda_b200 import gemm
+    A = _rand(200_000, 40, 3)   # (A X): N_nodes x in
+    G = _rand(200_000, 24, 4)   # N_nodes x out
+    ref = O.matmul(A.t().double(), G.double()).float()
+    out = gemm(A.to(cuda).t(), G.to(cuda), precision="fp32_simt")
+    assert O.rel_fro(out, ref) < TOL_FP32
+    out2 = gemm(A.to(cuda).t(), G.to(cuda), precision="fp32_simt")
+    assert torch.equal(out, out2)  # fixed summation order
+
+
+def test_simt_epilogue(cuda):
+    from graphcuda_b200 import gemm
+    A, B, b = _rand(300, 50, 5), _rand(50, 70, 6), _rand(1, 70, 7)[0]
+    pre = O.matmul(A, B) + b
+    Y, mask = gemm(A.to(cuda), B.to(cuda), bias=b.to(cuda), relu=True, want_mask=True, precision="fp32_simt")
+    assert O.rel_fro(Y, pre * (pre > 0)) < TOL_FP32
+    diff = mask.cpu() != (pre > 0).float()
+    assert float(pre[diff].abs().max() if diff.any() else 0.0) < 1e-5
+    Yt = gemm(A.to(cuda), B.to(cuda), transposed_out=True, precision="fp32_simt")
+    assert Yt.shape == (70, 300) and O.rel_fro(Yt.t(), O.matmul(A, B)) < TOL_FP32
+
+
+TC_SHAPES = [(128, 64, 32), (128, 256, 64), (256, 128, 96), (1000, 256, 100), (4096, 256, 256),
+             (777, 47, 256), (3000, 300, 130), (512, 512, 512), (129, 65, 33), (20000, 256, 128)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL_FP32), ("tf32", TOL_TF32)])
+def test_tensor_core_nt_form(cuda, shape, prec, tol):
+    """A row-major, B given as its transpose (N x K): both operands K-major, no
+    pre-pass except the low-part split."""
+    from graphcuda_b200 import gemm, ops
+    M, N, K = shape
+    K4 = (K + 3) // 4 * 4  # the tensor-core path needs 16-byte row pitches
+    A = _rand(M, K4, 11)[:, :K]
+    Bt = _rand(N, K4, 12)[:, :K]
+    ref = O.matmul(A.double(), Bt.t().double()).float()
+    Ag = _rand(M, K4, 11).to(cuda)[:, :K]
+    Btg = _rand(N, K4, 12).to(cuda)[:, :K]
+    out = gemm(Ag, Btg.t(), precision=prec)
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < tol, (O.rel_fro(out, ref), O.rel_max(out, ref))
+    assert O.rel_max(out, ref) < tol * 4
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (1, 1)])
+def test_tensor_core_other_layouts(cuda, ta, tb):
+    from graphcuda_b200 import gemm, ops
+    M, N, K = 1500, 200, 260
+    A, B = _rand(M, K, 21), _rand(K, N, 22)
+    ref = O.matmul(A.double(), B.double()).float()
+    Ag = (A.t().contiguous().to(cuda).t() if ta else A.to(cuda))
+    Bg = (B.t().contiguous().to(cuda).t() if tb else B.to(cuda))
+    out = gemm(Ag, Bg, precision="tf32x3")
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < TOL_FP32
+
+
+def test_tensor_core_epilogue(cuda):
+    from graphcuda_b200 import gemm, ops
+    A, B, b = _rand(1000, 128, 31), _rand(128, 256, 32), _rand(1, 256, 33)[0]
+    pre = O.matmul(A, B) + b
+    Y, mask = gemm(A.to(cuda), B.to(cuda), bias=b.to(cuda), relu=True, want_mask=True, precision="tf32x3")
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(Y, pre * (pre > 0)) < TOL_FP32
+    diff = mask.cpu() != (pre > 0).float()
+    assert float(pre[diff].abs().max() if diff.any() else 0.0) < 1e-3
+    Yt = gemm(A.to(cuda), B.to(cuda), transposed_out=True, precision="tf32x3")
+    assert Yt.shape == (256, 1000) and O.rel_fro(Yt.t(), O.matmul(A, B)) < TOL_FP32
+
+
+def test_tensor_core_matches_simt_on_device(cuda):
+    """Large persistent case (more tiles than SMs, both TMEM buffers cycling):
+    split-TF32 vs the fp32 CUDA-core kernel, on device."""
+    from graphcuda_b200 import gemm, ops
+    g = torch.Generator(device=cuda).manual_seed(0)
+    A = torch.rand(40_000, 256, generator=g, device=cuda) * 2 - 1
+    B = torch.rand(256, 256, generator=g, device=cuda) * 2 - 1
+    ref = gemm(A, B, precision="fp32_simt")
+    out = gemm(A, B, precision="tf32x3")
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < TOL_FP32
+    out1 = gemm(A, B, precision="tf32")
+    assert O.rel_fro(out1, ref) < TOL_TF32
+
+
+def test_auto_precision_dispatch(cuda):
+    from graphcuda_b200 import ops
+    small = torch.empty(2708, 1433, device=cuda), torch.empty(1433, 16, device=cuda)
+    big = torch.empty(169_343, 128, device=cuda), torch.empty(128, 256, device=cuda)
+    assert ops.gemm_path(*small) == "fp32_simt"
+    assert ops.gemm_path(*big) == "tf32x3"
+    assert ops.gemm_path(*big, precision="tf32") == "tf32"
+
+
+@pytest.mark.parametrize("name", ["matmul1", "matmul2", "matmul3", "matmul4", "gemm_cublas"])
+def test_reference_operator_names(cuda, name):
+    """Same names, shapes and error behaviour as the reference operators
+    (matmul1.cu:27-31, gemm_cublas.cu:3-7); matmul3's mixed tile shapes (M >= 128 > N)
+    and matmul4's N % 4 != 0 are correct here."""
+    import graphcuda
+    fn = getattr(graphcuda, name)
+    for (M, N, K) in [(512, 512, 512), (300, 64, 128), (130, 7, 50), (1024, 1024, 256)]:
+        A, B = _rand(M, K, M + N), _rand(K, N, K)
+        out = fn(A.to(cuda), B.to(cuda))
+        assert O.rel_fro(out, O.matmul(A, B)) < TOL_FP32
+    with pytest.raises(RuntimeError):
+        fn(torch.randn(4, 5, device=cuda), torch.randn(6, 4, device=cuda))
+    with pytest.raises(RuntimeError):
+        fn(torch.randn(4, 5), torch.randn(5, 4))
+    with pytest.raises(RuntimeError):
+        fn(torch.randn(4, 5, 2, device=cuda), torch.randn(5, 4, device=cuda))
+    # non-contiguous inputs are accepted (the reference copies them: gemm_cublas.cu:11-16)
+    A, B = _rand(40, 30, 1), _rand(50, 30, 2)
+    out = fn(A.to(cuda), B.to(cuda).t())
+    assert O.rel_fro(out, O.matmul(A, B.t())) < TOL_FP32
+
+
+@pytest.mark.parametrize("S", [512, 1024, 2048])
+def test_square_sweep(cuda, S):
+    import graphcuda
+    A, B = _rand(S, S, S), _rand(S, S, S + 1)
+    ref = O.matmul(A, B)
+    assert O.rel_fro(graphcuda.gemm_cublas(A.to(cuda), B.to(cuda)), ref) < TOL_FP32

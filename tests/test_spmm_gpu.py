@@ -1,0 +1,151 @@
+"""CSR aggregation kernel vs the oracle (torch.sparse.mm on CPU), through the
+C ABI (graphcuda_b200.adjacency -> gc_spmm_csr_f32)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gcn_oracle as O
+from tests.helpers import random_csr, to_gpu_csr
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4  # relative Frobenius / max, fp32 path
+
+
+@pytest.mark.parametrize("F", [1, 3, 7, 8, 16, 47, 48, 64, 100, 128, 200, 256, 260, 700])
+def test_feature_widths(cuda, F):
+    A = random_csr(500, 400, 9.0, seed=F, empty_rows=(0, 13, 499))
+    H = torch.randn(400, F, generator=torch.Generator().manual_seed(F + 1))
+    ref = O.spmm(A, H)
+    adj = to_gpu_csr(A, cuda)
+    out = adj.matmul(H.to(cuda))
+    assert O.rel_fro(out, ref) < TOL and O.rel_max(out, ref) < TOL
+    assert float(out[0].abs().max()) == 0.0 and float(out[499].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("F", [16, 100, 256])
+def test_long_rows_take_the_segment_path(cuda, F):
+    # rows of 1500 (one segment), 2048 (exactly one), 2049 (two), 9000 (five) non-zeros
+    A = random_csr(3000, 12000, 4.0, seed=3, long_rows=((7, 1500), (100, 2048), (101, 2049), (2999, 9000)))
+    H = torch.randn(12000, F, generator=torch.Generator().manual_seed(9))
+    ref = O.spmm(A, H)
+    adj = to_gpu_csr(A, cuda)
+    n_long, n_seg = adj.plan_counts()
+    assert n_long == 4 and n_seg == 1 + 1 + 2 + 5
+    out = adj.matmul(H.to(cuda))
+    assert O.rel_fro(out, ref) < TOL and O.rel_max(out, ref) < TOL
+    # same result without the plan (row-per-warp only)
+    from graphcuda_b200 import CSRAdjacency
+    plain = CSRAdjacency(adj.rowptr, adj.col, adj.val, adj.shape, build_plan=False)
+    out2 = plain.matmul(H.to(cuda))
+    assert O.rel_fro(out2, ref) < TOL
+
+
+def test_bias_relu_mask_accumulate(cuda):
+    A = random_csr(800, 800, 12.0, seed=5, long_rows=((3, 3000),))
+    g = torch.Generator().manual_seed(6)
+    H = torch.randn(800, 64, generator=g)
+    b = torch.randn(64, generator=g)
+    pre = O.spmm(A, H) + b
+    adj = to_gpu_csr(A, cuda)
+    Y, mask = adj.matmul(H.to(cuda), bias=b.to(cuda), relu=True, want_mask=True)
+    assert O.rel_fro(Y, pre * (pre > 0)) < TOL
+    # the mask may differ only where the pre-activation is within rounding of zero
+    diff = (mask.cpu() != (pre > 0).float())
+    assert float(pre[diff].abs().max() if diff.any() else 0.0) < 1e-5
+    base = torch.randn(800, 64, generator=g)
+    acc = base.to(cuda).clone()
+    adj.matmul(H.to(cuda), accumulate_into=acc)
+    assert O.rel_fro(acc, base + O.spmm(A, H)) < TOL
+
+
+def test_empty_matrix_and_zero_nnz(cuda):
+    from graphcuda_b200 import CSRAdjacency
+    rowptr = torch.zeros(11, dtype=torch.int32, device=cuda)
+    col = torch.empty(0, dtype=torch.int32, device=cuda)
+    val = torch.empty(0, dtype=torch.float32, device=cuda)
+    adj = CSRAdjacency(rowptr, col, val, (10, 6))
+    out = adj.matmul(torch.randn(6, 5, device=cuda))
+    assert out.shape == (10, 5) and float(out.abs().max()) == 0.0
+
+
+def test_deterministic_run_to_run(cuda):
+    A = random_csr(4000, 4000, 20.0, seed=8, long_rows=((1, 5000), (2, 2500)))
+    H = torch.randn(4000, 128, generator=torch.Generator().manual_seed(1)).to(cuda)
+    adj = to_gpu_csr(A, cuda)
+    a = adj.matmul(H)
+    b = adj.matmul(H)
+    assert torch.equal(a, b)
+
+
+def test_inf_in_unrelated_row_does_not_leak(cuda):
+    A = random_csr(64, 64, 3.0, seed=2)
+    dense = A.to_dense()
+    dense[:, 0] = 0  # nobody references row 0 of H
+    A = dense.to_sparse().coalesce()
+    H = torch.randn(64, 32)
+    H[0] = float("inf")
+    out = to_gpu_csr(A, cuda).matmul(H.to(cuda))
+    assert torch.isfinite(out).all()
+
+
+def test_spmm_cusparse_api(cuda):
+    """graphcuda.spmm_cusparse(sparseA, B): COO int64 input like the reference
+    (spmm_cusparse.cu:5-12,33-41) and the same error behaviour."""
+    import graphcuda
+    A = random_csr(300, 200, 6.0, seed=11)
+    B = torch.randn(200, 33, generator=torch.Generator().manual_seed(2))
+    out = graphcuda.spmm_cusparse(A.to(cuda), B.to(cuda))
+    assert O.rel_fro(out, O.spmm(A, B)) < TOL
+    # uncoalesced input is coalesced first (spmm_cusparse.cu:18)
+    idx = torch.cat([A.indices(), A.indices()[:, :50]], dim=1)
+    val = torch.cat([A.values(), A.values()[:50]])
+    dup = torch.sparse_coo_tensor(idx, val, A.shape).to(cuda)
+    out2 = graphcuda.spmm_cusparse(dup, B.to(cuda))
+    assert O.rel_fro(out2, O.spmm(dup.cpu().coalesce(), B)) < TOL
+    with pytest.raises(RuntimeError):
+        graphcuda.spmm_cusparse(A, B)  # CPU tensors are rejected
+    with pytest.raises(RuntimeError):
+        graphcuda.spmm_cusparse(A.to_dense().to(cuda), B.to(cuda))  # dense A is rejected by this operator
+    with pytest.raises(RuntimeError):
+        graphcuda.spmm_cusparse(A.to(cuda), torch.randn(201, 4, device=cuda))
+    # CSR overloads
+    out3 = graphcuda.spmm_cusparse(A.to_sparse_csr().to(cuda), B.to(cuda))
+    assert O.rel_fro(out3, O.spmm(A, B)) < TOL
+
+
+def test_golden_sparse_layer_aggregation(cuda, golden_dir):
+    g = np.load(os.path.join(golden_dir, "layer_sparse.npz"))
+    n = int(g["n"])
+    A = torch.sparse_coo_tensor(torch.stack([torch.from_numpy(g["rows"]), torch.from_numpy(g["cols"])]),
+                                torch.from_numpy(g["vals"]), (n, n)).coalesce()
+    X, W = torch.from_numpy(g["X"]), torch.from_numpy(g["W"])
+    adj = to_gpu_csr(A, cuda)
+    AX = adj.matmul(X.to(cuda))
+    assert O.rel_fro(AX.cpu() @ W, torch.from_numpy(g["Y0"])) < TOL
+
+
+def test_full_size_arxiv_like_graph(cuda):
+    """169,343 nodes / 1,166,243 undirected R-MAT edges, F = 128 and 256: direct
+    comparison with the CPU oracle plus the row-sum identity A 1 = rowsum(A)."""
+    from graphcuda_b200 import synth
+    from tests.helpers import sym_norm_graph
+    cfg = synth.CONFIGS["rmat_arxiv"]
+    n = cfg["nodes"]
+    e = synth.rmat_edges(cfg["scale"], n, cfg["edges"], cfg["seed"])
+    A = sym_norm_graph(e, n)
+    assert A._nnz() == 2 * cfg["edges"] + n
+    adj = to_gpu_csr(A, cuda)
+    assert adj.plan_counts()[0] > 0  # the heavy tail exists
+    for F in (128, 256):
+        H = synth.normal_features(n, F, seed=F)
+        out = adj.matmul(H.to(cuda))
+        ref = O.spmm(A, H)
+        assert O.rel_fro(out, ref) < TOL
+        assert O.rel_max(out, ref) < TOL
+    ones = torch.ones(n, 4, device=cuda)
+    rs = adj.matmul(ones)[:, 0].cpu()
+    ref_rs = torch.sparse.sum(A, dim=1).to_dense()
+    assert O.rel_max(rs, ref_rs) < 1e-5
