@@ -129,9 +129,13 @@ int simt_splits(int64_t M, int64_t N, int64_t K) {
   return int(std::max<int64_t>(1, std::min<int64_t>(splits, 512)));
 }
 
+// The first 256 bytes of every GEMM workspace hold the tensor-core path's
+// sticky error word; split-K partials start behind it.
+constexpr size_t kFlagBytes = 256;
+
 size_t simt_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int s = simt_splits(M, N, K);
-  return s > 1 ? size_t(s) * size_t(M) * size_t(N) * sizeof(float) : 0;
+  return s > 1 ? kFlagBytes + size_t(s) * size_t(M) * size_t(N) * sizeof(float) : 0;
 }
 
 int gemm_simt(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
@@ -142,8 +146,8 @@ int gemm_simt(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A,
   int splits = simt_splits(M, N, K);
   float* partial = nullptr;
   if (splits > 1) {
-    if (!workspace || workspace_bytes < size_t(splits) * M * N * sizeof(float)) splits = 1;
-    else partial = static_cast<float*>(workspace);
+    if (!workspace || workspace_bytes < kFlagBytes + size_t(splits) * M * N * sizeof(float)) splits = 1;
+    else partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + kFlagBytes);
   }
   int kps = int(ceil_div(ceil_div(K, splits), BK) * BK);
   if (kps <= 0) kps = BK;

@@ -34,3 +34,13 @@ def sym_norm_graph(edges_undirected, n):
     """Oracle-side normalised adjacency (coalesced COO, CPU) of an undirected edge list."""
     from graphcuda_b200 import synth
     return O.normalized_adjacency_coo(synth.symmetrize(edges_undirected), n)
+
+
+def untie(dY, pre_ref, rel=1e-4):
+    """Zeroes the upstream gradient where the reference pre-activation is within
+    `rel` of zero (relative to its largest magnitude).  The ReLU mask of such an
+    element is decided by rounding, so two correct implementations may disagree
+    on it; everywhere else the gradient comparison is unaffected."""
+    dY = dY.clone()
+    dY[pre_ref.abs() < rel * pre_ref.abs().max()] = 0
+    return dY
