@@ -20,13 +20,10 @@ int resolve(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda, int6
   }
   if (precision != GC_PREC_AUTO) return gc::fail(GC_ERR_INVALID, "unknown precision %d", precision);
   if (!tc_ok) return GC_PREC_FP32_SIMT;
-  // Small problems are launch-bound and stay on the CUDA cores (bit-stable);
-  // so do few-tile / huge-K shapes (weight gradients), which the CUDA-core
-  // kernel splits along K.
+  // Small problems are launch-bound and stay on the CUDA cores (bit-stable).
+  // Few-tile / huge-K shapes (weight gradients) are split along K on either path.
   const double flops = 2.0 * double(M) * double(N) * double(K);
-  if (flops < double(1ull << 30) || M < 512) return GC_PREC_FP32_SIMT;
-  const int64_t tiles = gc::ceil_div(M, 128) * gc::ceil_div(N, 256);
-  if (tiles < 32 && K >= 8192) return GC_PREC_FP32_SIMT;
+  if (flops < double(1ull << 30)) return GC_PREC_FP32_SIMT;
   return GC_PREC_TF32X3;
 }
 

@@ -118,25 +118,42 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of
-// 128 bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor
-// version 1 (sm_100), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+// Shared-memory matrix descriptors (version 1 = sm_100).  Tiles are rows of
+// 128 bytes as TMA writes them:
+//  * K-major operand (layout type 2, SWIZZLE_128B, 16-byte atoms): a row is 32
+//    consecutive K values of one M/N index; 8-row groups follow each other
+//    every 1024 bytes (stride byte offset); one MMA (K = 8) reads 32 bytes of
+//    every row, so successive k-steps advance the start address by 32 bytes.
+//  * MN-major operand (layout type 1, SWIZZLE_128B with 32-byte atoms -- the
+//    only swizzle kind::tf32 accepts for transposed 32-bit operands; with the
+//    16-byte-atom swizzle or no swizzle the MMA returns zeros): a row is 32
+//    consecutive M/N values at one k; the 32-byte unit index is XORed with
+//    k % 4; groups of 4 k-rows are 512 bytes apart (stride byte offset) and
+//    32-column chunks `mn_chunk` bytes apart (leading byte offset); one MMA
+//    reads 8 k-rows = 1024 bytes, the advance per k-step.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
   uint64_t d = 0;
   d |= uint64_t((saddr & 0x3FFFFu) >> 4);
-  d |= uint64_t(1024u >> 4) << 32;
+  d |= uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= uint64_t(1) << 46;
-  d |= uint64_t(2) << 61;
+  d |= uint64_t(layout_type) << 61;
   return d;
 }
+__device__ __forceinline__ uint64_t smem_desc_operand(uint32_t saddr, bool mn_major, uint32_t mn_chunk) {
+  return mn_major ? smem_desc(saddr, mn_chunk, 512u, 1u) : smem_desc(saddr, 0u, 1024u, 2u);
+}
 
-// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major.
-__host__ __device__ constexpr uint32_t make_idesc(int bn) {
-  return (1u << 4)                    // D format: F32
-         | (2u << 7)                  // A format: TF32
-         | (2u << 10)                 // B format: TF32
-         | (uint32_t(bn >> 3) << 17)  // N / 8
-         | (uint32_t(BM >> 4) << 24); // M / 16
+// Instruction descriptor for kind::tf32 with fp32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc(int bn, bool a_mn, bool b_mn) {
+  return (1u << 4)                      // D format: F32
+         | (2u << 7)                    // A format: TF32
+         | (2u << 10)                   // B format: TF32
+         | (uint32_t(a_mn ? 1 : 0) << 15)  // A major: 0 = K, 1 = MN
+         | (uint32_t(b_mn ? 1 : 0) << 16)  // B major
+         | (uint32_t(bn >> 3) << 17)    // N / 8
+         | (uint32_t(BM >> 4) << 24);   // M / 16
 }
 
 struct TcParams {
@@ -144,8 +161,11 @@ struct TcParams {
   float* C;
   int64_t ldc;
   gc::GemmEpilogue ep;
-  int* flag;  // global word set when a wait ran out
-  int vec_store;  // rows of C are 16-byte aligned
+  int* flag;       // global word set when a wait ran out
+  int vec_store;   // rows of C are 16-byte aligned
+  int splits;      // > 1: K is cut into `splits` ranges of kb_per_split k-blocks,
+  int kb_per_split;  //    raw partial tiles go to partial[split][M][N]
+  float* partial;
 };
 
 template <int BN, int PASSES>
@@ -159,12 +179,18 @@ struct Cfg {
   static_assert(kStages >= 2, "need at least two stages");
 };
 
-template <int BN, int PASSES>
+// A_MN / B_MN: the operand is MN-major in global memory (A stored K x M,
+// B stored K x N) and is staged MN-major, 32 columns per TMA box.
+// CONV_B: B_lo is produced in shared memory by the converter warps like A_lo
+// (large B operands: activations, gradients); otherwise it is loaded from a
+// pre-split copy (weights).
+template <int BN, int PASSES, bool A_MN, bool B_MN, bool CONV_B>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapBlo, TcParams p) {
   using C_ = Cfg<BN, PASSES>;
   constexpr int S = C_::kStages;
+  constexpr bool kConvB = CONV_B && PASSES == 3;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -186,8 +212,19 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int num_tiles = tiles_m * tiles_n;
-  const int nkb = (p.K + BK - 1) / BK;
+  const int nkb_total = (p.K + BK - 1) / BK;
+  const int splits = p.splits > 1 ? p.splits : 1;
+  const int kb_per = splits > 1 ? p.kb_per_split : nkb_total;
+  // work item = (split, m tile, n tile), n fastest
+  const int num_items = tiles_m * tiles_n * splits;
+  auto item_coords = [&](int item, int& m0, int& n0, int& kb0, int& kb1, int& split) {
+    const int t = item % (tiles_m * tiles_n);
+    split = item / (tiles_m * tiles_n);
+    m0 = (t / tiles_n) * BM;
+    n0 = (t % tiles_n) * BN;
+    kb0 = split * kb_per;
+    kb1 = min(nkb_total, kb0 + kb_per);
+  };
 
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -215,20 +252,34 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+      constexpr uint32_t kTx = C_::kABytes + ((PASSES == 3 && !kConvB) ? 2 : 1) * C_::kBBytes;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        int m0, n0, kb0, kb1, split;
+        item_coords(item, m0, n0, kb0, kb1, split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_p)) { ok = false; break; }
-          mbar_expect_tx(bar_full(s), C_::kABytes + (PASSES == 3 ? 2 : 1) * C_::kBBytes);
-          tma_load_2d(sA(s), &mapA, kb * BK, m0, bar_full(s));
-          tma_load_2d(sB(s), &mapB, kb * BK, n0, bar_full(s));
-          if (PASSES == 3) tma_load_2d(sBlo(s), &mapBlo, kb * BK, n0, bar_full(s));
+          mbar_expect_tx(bar_full(s), kTx);
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c)
+              tma_load_2d(sA(s) + c * (BK * 128), &mapA, m0 + c * 32, kb * BK, bar_full(s));
+          } else {
+            tma_load_2d(sA(s), &mapA, kb * BK, m0, bar_full(s));
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_2d(sB(s) + c * (BK * 128), &mapB, n0 + c * 32, kb * BK, bar_full(s));
+          } else {
+            tma_load_2d(sB(s), &mapB, kb * BK, n0, bar_full(s));
+            if (PASSES == 3 && !kConvB) tma_load_2d(sBlo(s), &mapBlo, kb * BK, n0, bar_full(s));
+          }
         }
       }
       // Drain: every copy issued must have landed before the CTA may exit.
-      // `it` loads were issued; the last min(S, it) of them may be in flight.
+      // `it` stages were issued; the last min(S, it) of them may be in flight.
       const uint32_t pending = it < uint32_t(S) ? it : uint32_t(S);
       for (uint32_t j = 0; j < pending; ++j) {
         const uint32_t q = it - 1 - j;
@@ -242,33 +293,41 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BN);
+      constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+      constexpr uint32_t kMnLbo = BK * 128;  // bytes between 32-column chunks of an MN-major tile
+      constexpr uint32_t kAStep = A_MN ? 1024u : uint32_t(UMMA_K * 4);  // start-address advance per k-step
+      constexpr uint32_t kBStep = B_MN ? 1024u : uint32_t(UMMA_K * 4);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++tcount) {
+        int m0, n0, kb0, kb1, split;
+        item_coords(item, m0, n0, kb0, kb1, split);
         const int b = tcount & 1;
         const uint32_t bph = (tcount >> 1) & 1u;
         if (!mbar_wait(bar_tempty(b), bph ^ 1u, abort_p)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + uint32_t(b * BN);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(bar_full(s), ph, abort_p)) { ok = false; break; }
           if (PASSES == 3 && !mbar_wait(bar_conv(s), ph, abort_p)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = smem_desc_k128(sA(s)), db = smem_desc_k128(sB(s));
-          const uint64_t dal = smem_desc_k128(sAlo(s)), dbl = smem_desc_k128(sBlo(s));
+          const uint64_t da = smem_desc_operand(sA(s), A_MN, kMnLbo);
+          const uint64_t db = smem_desc_operand(sB(s), B_MN, kMnLbo);
+          const uint64_t dal = smem_desc_operand(sAlo(s), A_MN, kMnLbo);
+          const uint64_t dbl = smem_desc_operand(sBlo(s), B_MN, kMnLbo);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adv = uint64_t((k * UMMA_K * 4) >> 4);  // bytes >> 4 in the address field
-            const uint32_t first = (kb | k) ? 1u : 0u;
+            const uint64_t aa = uint64_t((k * kAStep) >> 4);  // byte offset >> 4 into the address field
+            const uint64_t ab = uint64_t((k * kBStep) >> 4);
+            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
             if (PASSES == 3) {
-              umma_tf32(d_tmem, dal + adv, db + adv, idesc, first);
-              umma_tf32(d_tmem, da + adv, dbl + adv, idesc, 1u);
-              umma_tf32(d_tmem, da + adv, db + adv, idesc, 1u);
+              umma_tf32(d_tmem, dal + aa, db + ab, idesc, acc);
+              umma_tf32(d_tmem, da + aa, dbl + ab, idesc, 1u);
+              umma_tf32(d_tmem, da + aa, db + ab, idesc, 1u);
             } else {
-              umma_tf32(d_tmem, da + adv, db + adv, idesc, first);
+              umma_tf32(d_tmem, da + aa, db + ab, idesc, acc);
             }
           }
           umma_commit(bar_empty(s));  // frees the stage once these MMAs have read it
@@ -281,14 +340,22 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const int q = warp - 4;  // TMEM lane quarter == warp id % 4
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++tcount) {
+      int m0, n0, kb0, kb1, split;
+      item_coords(item, m0, n0, kb0, kb1, split);
       const int b = tcount & 1;
       const uint32_t bph = (tcount >> 1) & 1u;
       if (!mbar_wait(bar_tfull(b), bph, abort_p)) { ok = false; break; }
       tc_fence_after();
       const int gm = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN);
+      // split-K: raw partial tile, row-major M x N, no epilogue
+      const bool raw_out = splits > 1;
+      float* Cb = raw_out ? p.partial + int64_t(split) * p.M * p.N : p.C;
+      const int64_t ldc = raw_out ? int64_t(p.N) : p.ldc;
+      gc::GemmEpilogue ep = p.ep;
+      if (raw_out) ep = gc::GemmEpilogue{nullptr, nullptr, 0, 0};
+      const bool vec = raw_out ? (p.N % 4 == 0) : (p.vec_store != 0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -296,30 +363,30 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         tmem_ld_wait();
         const int gn0 = n0 + c * 32;
         if (gn0 >= p.N) continue;  // uniform across the warp
-        if (p.ep.transposed) {
+        if (ep.transposed) {
           // lanes hold consecutive m: a column of C is a contiguous run of C^T
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int gn = gn0 + j;
-            if (gn < p.N && gm < p.M) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, p.C, p.ldc, p.ep);
+            if (gn < p.N && gm < p.M) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
           }
         } else if (gm < p.M) {
-          if (p.vec_store && gn0 + 32 <= p.N) {
-            float* crow = p.C + int64_t(gm) * p.ldc + gn0;
-            float* mrow = p.ep.mask ? p.ep.mask + int64_t(gm) * p.ldc + gn0 : nullptr;
+          if (vec && gn0 + 32 <= p.N) {
+            float* crow = Cb + int64_t(gm) * ldc + gn0;
+            float* mrow = ep.mask ? ep.mask + int64_t(gm) * ldc + gn0 : nullptr;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
                                      __uint_as_float(r[j + 3]));
-              if (p.ep.bias) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.ep.bias + gn0 + j));
+              if (ep.bias) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + j));
                 v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
               }
-              if (p.ep.relu || mrow) {
+              if (ep.relu || mrow) {
                 const float4 mk = make_float4(v.x > 0.f ? 1.f : 0.f, v.y > 0.f ? 1.f : 0.f, v.z > 0.f ? 1.f : 0.f,
                                               v.w > 0.f ? 1.f : 0.f);
                 if (mrow) *reinterpret_cast<float4*>(mrow + j) = mk;
-                if (p.ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
+                if (ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
               }
               *reinterpret_cast<float4*>(crow + j) = v;
             }
@@ -327,7 +394,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int gn = gn0 + j;
-              if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, p.C, p.ldc, p.ep);
+              if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
             }
           }
         }
@@ -339,24 +406,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   } else if (warp >= 8 && PASSES == 3) {
     // ------------------------------------------------------------ converter
     const int ct = threadIdx.x - 256;  // 0..127
+    constexpr int kVecs = (C_::kABytes + (kConvB ? C_::kBBytes : 0)) / 16;  // A (and B) are contiguous in a stage
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      int m0, n0, kb0, kb1, split;
+      item_coords(item, m0, n0, kb0, kb1, split);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         if (!mbar_wait(bar_full(s), ph, abort_p)) { ok = false; break; }
         const float4* src = reinterpret_cast<const float4*>(smem + s * C_::kStageBytes);
         float4* dst = reinterpret_cast<float4*>(smem + s * C_::kStageBytes + C_::kABytes + C_::kBBytes);
-#pragma unroll
-        for (int i = 0; i < C_::kABytes / 16 / 128; ++i) {
-          const float4 v = src[ct + i * 128];
+#pragma unroll 8
+        for (int i = ct; i < kVecs; i += 128) {
+          const float4 v = src[i];
           float4 lo;
           lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
           lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
           lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
           lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-          dst[ct + i * 128] = lo;
+          dst[i] = lo;
         }
         fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
         __syncwarp();
@@ -402,6 +472,18 @@ transpose_kernel(const float* __restrict__ in, int64_t ldin, float* __restrict__
   }
 }
 
+// C = sum over splits of partial[split] (in split order), then the epilogue.
+__global__ void __launch_bounds__(256)
+tc_splitk_reduce_kernel(int M, int N, int splits, const float* __restrict__ partial, float* __restrict__ C,
+                        int64_t ldc, gc::GemmEpilogue ep) {
+  const int64_t total = int64_t(M) * N;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+    float s = partial[i];
+    for (int z = 1; z < splits; ++z) s += partial[int64_t(z) * total + i];
+    gc::epilogue_store(s, int(i / N), int(i % N), C, ldc, ep);
+  }
+}
+
 // ------------------------------------------------------------------ host
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -419,17 +501,23 @@ EncodeFn get_encode() {
   return fn;
 }
 
-// Tensor map over a K-major operand: `rows` rows of `K` fp32, row pitch ld;
-// box = 32 fp32 (128 bytes, the swizzle span) x box_rows.
-int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+// Tensor map over a row-major fp32 matrix of `rows` rows and `cols` columns
+// (row pitch ld): box = 32 columns (128 bytes, the swizzle span) x box_rows.
+// K-major operands pass (rows = M or N, cols = K) and take the 16-byte-atom
+// 128-byte swizzle; MN-major operands pass (rows = K, cols = M or N) and take
+// the 32-byte-atom one.
+int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows,
+             bool mn_major) {
   EncodeFn enc = get_encode();
   if (!enc) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
   cuuint64_t strides[1] = {cuuint64_t(ld) * 4};
-  cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+  cuuint32_t box[2] = {32u, cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
   return GC_OK;
@@ -445,17 +533,69 @@ int pick_bn(int64_t N) {
   return (rem == 0 || rem > 128) ? 256 : 128;
 }
 
-template <int BN, int PASSES>
+// B operands up to this many elements (weights) are re-laid K-major and
+// pre-split once per call; larger ones are consumed in place.
+constexpr int64_t kSmallB = int64_t(1) << 21;
+
+struct Plan {
+  bool transpose_a;  // A given K x M, re-laid M x K in the workspace
+  bool a_mn;         // A consumed MN-major in place
+  bool transpose_b;  // B given K x N, re-laid N x K in the workspace
+  bool b_mn;         // B consumed MN-major in place
+  bool conv_b;       // B_lo made in shared memory (else pre-split into the workspace)
+  int bn;
+  int splits, kb_per_split;
+};
+
+Plan make_plan(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int passes) {
+  Plan pl{};
+  pl.bn = pick_bn(N);
+  const bool small_b = N * K <= kSmallB;
+  if (ta) {
+    // weight-gradient form: consume A in place; B in place too unless it is a small N x K matrix
+    pl.a_mn = true;
+  }
+  if (!tb) {
+    if (small_b && !ta) pl.transpose_b = true;
+    else pl.b_mn = true;
+  }
+  // the MN-major kernel variant is instantiated for (A_MN, B_MN) = (1,1) and (0,1); (1,0) re-lays A
+  if (pl.a_mn && !pl.b_mn) {
+    pl.a_mn = false;
+    pl.transpose_a = true;
+  }
+  pl.conv_b = pl.b_mn || !(small_b);
+  if (passes != 3) pl.conv_b = pl.b_mn;  // selects the template only
+  const int64_t tiles = gc::ceil_div(M, BM) * gc::ceil_div(N, pl.bn);
+  const int64_t nkb = gc::ceil_div(K, BK);
+  int64_t splits = 1;
+  if (tiles * 2 <= gc::kNumSMs && nkb >= 64) splits = std::min<int64_t>(gc::kNumSMs / tiles, nkb / 16);
+  splits = std::max<int64_t>(1, splits);
+  pl.kb_per_split = int(gc::ceil_div(nkb, splits));
+  pl.splits = int(gc::ceil_div(nkb, pl.kb_per_split));
+  return pl;
+}
+
+template <int BN, int PASSES, bool A_MN, bool B_MN, bool CONV_B>
 int launch_tc(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mBlo, const TcParams& p,
               cudaStream_t st) {
   using C_ = Cfg<BN, PASSES>;
-  cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       C_::kSmemBytes);
+  auto kern = gemm_tf32_kernel<BN, PASSES, A_MN, B_MN, CONV_B>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes);
   if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  const int64_t tiles = gc::ceil_div(p.M, BM) * gc::ceil_div(p.N, BN);
-  const unsigned grid = unsigned(std::min<int64_t>(tiles, gc::kNumSMs));
-  gemm_tf32_kernel<BN, PASSES><<<grid, kThreads, C_::kSmemBytes, st>>>(mA, mB, mBlo, p);
+  const int64_t items = gc::ceil_div(p.M, BM) * gc::ceil_div(p.N, BN) * (p.splits > 1 ? p.splits : 1);
+  const unsigned grid = unsigned(std::min<int64_t>(items, gc::kNumSMs));
+  kern<<<grid, kThreads, C_::kSmemBytes, st>>>(mA, mB, mBlo, p);
   return gc::check_launch("gemm_tf32_kernel");
+}
+
+template <int BN, int PASSES>
+int launch_layout(const Plan& pl, const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mBlo,
+                  const TcParams& p, cudaStream_t st) {
+  if (pl.a_mn && pl.b_mn) return launch_tc<BN, PASSES, true, true, true>(mA, mB, mBlo, p, st);
+  if (pl.b_mn) return launch_tc<BN, PASSES, false, true, true>(mA, mB, mBlo, p, st);
+  if (pl.conv_b && PASSES == 3) return launch_tc<BN, PASSES, false, false, true>(mA, mB, mBlo, p, st);
+  return launch_tc<BN, PASSES, false, false, false>(mA, mB, mBlo, p, st);
 }
 
 }  // namespace
@@ -466,20 +606,23 @@ bool tc_supported(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda
   (void)ldc;
   if (M <= 0 || N <= 0 || K <= 0) return false;
   if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return false;
-  // operands read in place must have 16-byte aligned row pitch; transposed
-  // operands are re-laid into the workspace with a padded pitch
-  if (!ta && (lda % 4 != 0)) return false;
-  if (tb && (ldb % 4 != 0)) return false;
+  // operands consumed in place need 16-byte aligned row pitches; operands that
+  // are re-laid into the workspace get a padded pitch there
+  const Plan pl = make_plan(ta, tb, M, N, K, 3);
+  if (!pl.transpose_a && lda % 4 != 0) return false;
+  if (!pl.transpose_b && ldb % 4 != 0) return false;
   return true;
 }
 
-// Workspace layout: [flag: 256 B][A^T (transA)][B^T (!transB)][B_lo (3 passes)]
+// Workspace layout: [flag: 256 B][A^T][B^T][B_lo][split-K partials]
 size_t tc_workspace_bytes(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int passes) {
+  const Plan pl = make_plan(ta, tb, M, N, K, passes);
   size_t b = 256;
   const size_t kp = size_t(round4(K));
-  if (ta) b += align256(size_t(M) * kp * 4);
-  if (!tb) b += align256(size_t(N) * kp * 4);
-  if (passes == 3) b += align256(size_t(N) * kp * 4);
+  if (pl.transpose_a) b += align256(size_t(M) * kp * 4);
+  if (pl.transpose_b) b += align256(size_t(N) * kp * 4);
+  if (passes == 3 && !pl.conv_b) b += align256(size_t(N) * kp * 4);
+  if (pl.splits > 1) b += align256(size_t(pl.splits) * size_t(M) * size_t(N) * 4);
   return b;
 }
 
@@ -489,6 +632,7 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
   if (!workspace || workspace_bytes < tc_workspace_bytes(ta, tb, M, N, K, passes))
     return fail(GC_ERR_WORKSPACE, "gemm_tc: workspace missing or smaller than gc_gemm_workspace_bytes()");
   if (!aligned16(workspace)) return fail(GC_ERR_INVALID, "gemm_tc: workspace must be 16-byte aligned");
+  const Plan pl = make_plan(ta, tb, M, N, K, passes);
   char* ws = static_cast<char*>(workspace);
   int* flag = reinterpret_cast<int*>(ws);
   ws += 256;
@@ -496,41 +640,52 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
   const unsigned tgrid = kNumSMs * 8;
   int rc;
 
-  const float* Ak = A;  // K-major view of A: M rows of K
-  int64_t ldak = lda;
-  if (ta) {
+  const float* Aop = A;
+  int64_t lda_op = lda;
+  if (pl.transpose_a) {
     float* At = reinterpret_cast<float*>(ws);
     ws += align256(size_t(M) * kp * 4);
     transpose_kernel<<<tgrid, 256, 0, st>>>(A, lda, At, kp, int(K), int(M));
     if ((rc = check_launch("transpose A")) != GC_OK) return rc;
-    Ak = At;
-    ldak = kp;
+    Aop = At;
+    lda_op = kp;
   }
-  const float* Bk = B;  // K-major view of B: N rows of K
-  int64_t ldbk = ldb;
-  if (!tb) {
+  const float* Bop = B;
+  int64_t ldb_op = ldb;
+  if (pl.transpose_b) {
     float* Bt = reinterpret_cast<float*>(ws);
     ws += align256(size_t(N) * kp * 4);
     transpose_kernel<<<tgrid, 256, 0, st>>>(B, ldb, Bt, kp, int(K), int(N));
     if ((rc = check_launch("transpose B")) != GC_OK) return rc;
-    Bk = Bt;
-    ldbk = kp;
+    Bop = Bt;
+    ldb_op = kp;
   }
-  const float* Blo = Bk;
-  if (passes == 3) {
+  const float* Blo = Bop;
+  int64_t ldblo = ldb_op;
+  if (passes == 3 && !pl.conv_b) {
     float* bl = reinterpret_cast<float*>(ws);
     ws += align256(size_t(N) * kp * 4);
-    split_lo_kernel<<<tgrid, 256, 0, st>>>(Bk, ldbk, bl, kp, int(N), int(K));
+    split_lo_kernel<<<tgrid, 256, 0, st>>>(Bop, ldb_op, bl, kp, int(N), int(K));
     if ((rc = check_launch("split B")) != GC_OK) return rc;
     Blo = bl;
+    ldblo = kp;
   }
-  if (!aligned16(Ak) || !aligned16(Bk)) return fail(GC_ERR_UNSUPPORTED, "gemm_tc: operand base not 16-byte aligned");
+  float* partial = nullptr;
+  if (pl.splits > 1) {
+    partial = reinterpret_cast<float*>(ws);
+    ws += align256(size_t(pl.splits) * size_t(M) * size_t(N) * 4);
+  }
+  if (!aligned16(Aop) || !aligned16(Bop)) return fail(GC_ERR_UNSUPPORTED, "gemm_tc: operand base not 16-byte aligned");
 
-  const int bn = pick_bn(N);
   CUtensorMap mA, mB, mBlo;
-  if ((rc = make_map(&mA, Ak, M, K, ldak, BM)) != GC_OK) return rc;
-  if ((rc = make_map(&mB, Bk, N, K, ldbk, bn)) != GC_OK) return rc;
-  if ((rc = make_map(&mBlo, Blo, N, K, passes == 3 ? kp : ldbk, bn)) != GC_OK) return rc;
+  if (pl.a_mn) rc = make_map(&mA, Aop, K, M, lda_op, BK, true);
+  else rc = make_map(&mA, Aop, M, K, lda_op, BM, false);
+  if (rc != GC_OK) return rc;
+  if (pl.b_mn) rc = make_map(&mB, Bop, K, N, ldb_op, BK, true);
+  else rc = make_map(&mB, Bop, N, K, ldb_op, pl.bn, false);
+  if (rc != GC_OK) return rc;
+  if (pl.b_mn) mBlo = mB;
+  else if ((rc = make_map(&mBlo, Blo, N, K, ldblo, pl.bn, false)) != GC_OK) return rc;
 
   TcParams p;
   p.M = int(M);
@@ -544,12 +699,26 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
                  (!ep.bias || aligned16(ep.bias)))
                     ? 1
                     : 0;
-#define GC_TC(BN_)                                                                 \
-  (passes == 3 ? launch_tc<BN_, 3>(mA, mB, mBlo, p, st) : launch_tc<BN_, 1>(mA, mB, mBlo, p, st))
-  if (bn == 64) return GC_TC(64);
-  if (bn == 128) return GC_TC(128);
-  return GC_TC(256);
-#undef GC_TC
+  p.splits = pl.splits;
+  p.kb_per_split = pl.kb_per_split;
+  p.partial = partial;
+  if (passes == 3) {
+    if (pl.bn == 64) rc = launch_layout<64, 3>(pl, mA, mB, mBlo, p, st);
+    else if (pl.bn == 128) rc = launch_layout<128, 3>(pl, mA, mB, mBlo, p, st);
+    else rc = launch_layout<256, 3>(pl, mA, mB, mBlo, p, st);
+  } else {
+    if (pl.bn == 64) rc = launch_layout<64, 1>(pl, mA, mB, mBlo, p, st);
+    else if (pl.bn == 128) rc = launch_layout<128, 1>(pl, mA, mB, mBlo, p, st);
+    else rc = launch_layout<256, 1>(pl, mA, mB, mBlo, p, st);
+  }
+  if (rc != GC_OK) return rc;
+  if (pl.splits > 1) {
+    const int64_t total = M * N;
+    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 256), kNumSMs * 8));
+    tc_splitk_reduce_kernel<<<g, 256, 0, st>>>(int(M), int(N), pl.splits, partial, C, ldc, ep);
+    rc = check_launch("gemm_tc split-K reduce");
+  }
+  return rc;
 }
 
 }  // namespace gc

@@ -33,6 +33,27 @@ def choose_order(in_dim: int, out_dim: int, symmetric: bool) -> str:
     return "transform_first" if (out_dim < in_dim and symmetric) else "aggregate_first"
 
 
+# Transform-first layers with an output width that is not a multiple of 4
+# (47 classes) run on a zero-padded width so every row pitch is 16-byte aligned
+# (vector gathers in the aggregation, TMA in the tensor-core GEMMs).  Small
+# problems are not worth the copies.
+_PAD_MIN_WORK = 1 << 27
+
+
+def _padded_width(n_rows: int, in_dim: int, out_dim: int) -> int:
+    if out_dim % 4 == 0 or n_rows * in_dim * out_dim < _PAD_MIN_WORK:
+        return out_dim
+    return (out_dim + 3) // 4 * 4
+
+
+def _pad_cols(t: torch.Tensor, width: int) -> torch.Tensor:
+    if t.size(-1) == width:
+        return t
+    out = t.new_zeros(t.shape[:-1] + (width,))
+    out[..., :t.size(-1)] = t
+    return out
+
+
 def _adj_matmul(adj, H, precision, **kw):
     from .adjacency import DenseAdjacency
     if isinstance(adj, DenseAdjacency):
@@ -52,9 +73,16 @@ def layer_forward(X, adj, W, bias: Optional[torch.Tensor], relu: bool, *, want_m
         r = ops.gemm(AX, W, bias=bias, relu=relu, want_mask=want_mask, precision=precision)
         Y, mask = r if want_mask else (r, None)
         return Y, mask, (order, AX)
-    H = ops.gemm(X, W, precision=precision)
-    r = _adj_matmul(adj, H, precision, bias=bias, relu=relu, want_mask=want_mask)
+    out_dim = W.size(1)
+    width = _padded_width(X.size(0), W.size(0), out_dim)
+    Wp = _pad_cols(W, width)
+    bp = _pad_cols(bias, width) if bias is not None else None
+    H = ops.gemm(X, Wp, precision=precision)
+    r = _adj_matmul(adj, H, precision, bias=bp, relu=relu, want_mask=want_mask)
     Y, mask = r if want_mask else (r, None)
+    if width != out_dim:  # views on the padded buffers; the pad columns hold zeros
+        Y = Y[:, :out_dim]
+        mask = mask[:, :out_dim] if mask is not None else None
     return Y, mask, (order, None)
 
 
@@ -69,6 +97,17 @@ def layer_backward(dY, X, adj, W, relu: bool, Y, saved, *, need_dX: bool = True,
     dX = dW = db = None
     if need_db:
         db = G.sum(0)
+    out_dim = W.size(1)
+    width = _padded_width(X.size(0), W.size(0), out_dim) if order == "transform_first" else out_dim
+    if width != out_dim:
+        Gp = _pad_cols(G, width)
+        Wp = _pad_cols(W, width)
+        S = _adj_matmul(adj, Gp, precision)
+        if need_dW:
+            dW = ops.gemm(X.t(), S, precision=precision)[:, :out_dim]
+        if need_dX:
+            dX = ops.gemm(S, Wp.t(), precision=precision)
+        return dX, dW, db
     if order == "aggregate_first":
         if need_dW:
             dW = ops.gemm(AX.t(), G, precision=precision)

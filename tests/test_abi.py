@@ -81,6 +81,7 @@ def test_precision_resolution_is_host_logic():
     # unaligned row pitch of an operand read in place -> CUDA cores under AUTO, error when forced
     assert L.gc_gemm_resolve_precision(0, 0, 169343, 256, 127, 127, 256, 256, P.PREC_AUTO) == P.PREC_FP32_SIMT
     assert L.gc_gemm_resolve_precision(0, 0, 169343, 256, 127, 127, 256, 256, P.PREC_TF32) == -2
-    # weight-gradient shape (few tiles, huge K) stays on the split-K CUDA-core kernel
-    assert L.gc_gemm_resolve_precision(1, 0, 256, 256, 2449029, 256, 256, 256, P.PREC_AUTO) == P.PREC_FP32_SIMT
+    # weight-gradient shape (few tiles, huge K): tensor cores with split-K, operands read in place
+    assert L.gc_gemm_resolve_precision(1, 0, 256, 256, 2449029, 256, 256, 256, P.PREC_AUTO) == P.PREC_TF32X3
+    assert L.gc_gemm_resolve_precision(1, 0, 256, 47, 2449029, 256, 47, 47, P.PREC_AUTO) == P.PREC_FP32_SIMT
     assert L.gc_gemm_resolve_precision(0, 0, 8192, 8192, 8192, 8192, 8192, 8192, P.PREC_FP32_SIMT) == P.PREC_FP32_SIMT

@@ -90,6 +90,44 @@ def test_tensor_core_other_layouts(cuda, ta, tb):
     assert O.rel_fro(out, ref) < TOL_FP32
 
 
+@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL_FP32), ("tf32", TOL_TF32)])
+@pytest.mark.parametrize("shape", [(256, 256, 100_000), (100, 256, 70_001), (256, 48, 50_000), (128, 64, 4096),
+                                   (300, 200, 20_000)])
+def test_tensor_core_weight_gradient_form(cuda, shape, prec, tol):
+    """C = A^T B with A stored K x M and B stored K x N (both read in place,
+    MN-major in shared memory), K split across CTAs, partials reduced in order."""
+    from graphcuda_b200 import gemm, ops
+    M, N, K = shape
+    A = _rand(K, M, 41)
+    B = _rand(K, N, 42)
+    ref = O.matmul(A.t().double(), B.double()).float()
+    Ag, Bg = A.to(cuda), B.to(cuda)
+    out = gemm(Ag.t(), Bg, precision=prec)
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < tol, (O.rel_fro(out, ref), O.rel_max(out, ref))
+    out2 = gemm(Ag.t(), Bg, precision=prec)
+    assert torch.equal(out, out2)  # split-K partials are added in a fixed order
+
+
+@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL_FP32), ("tf32", TOL_TF32)])
+def test_tensor_core_large_b_operands(cuda, prec, tol):
+    """B too large to be re-laid: consumed in place, MN-major (A @ B with B
+    stored K x N, e.g. a dense adjacency times features) or K-major (A @ Bt^T),
+    its low part made in shared memory."""
+    from graphcuda_b200 import gemm, ops
+    A, B = _rand(1024, 6000, 51), _rand(6000, 512, 52)          # N*K = 3.07 M elements
+    ref = O.matmul(A.double(), B.double()).float()
+    out = gemm(A.to(cuda), B.to(cuda), precision=prec)
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < tol, O.rel_fro(out, ref)
+    Bt = _rand(1100, 2100, 53)                                    # N x K, 2.31 M elements
+    A2 = _rand(3000, 2100, 54)
+    ref2 = O.matmul(A2.double(), Bt.t().double()).float()
+    out2 = gemm(A2.to(cuda), Bt.to(cuda).t(), precision=prec)
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out2, ref2) < tol, O.rel_fro(out2, ref2)
+
+
 def test_tensor_core_epilogue(cuda):
     from graphcuda_b200 import gemm, ops
     A, B, b = _rand(1000, 128, 31), _rand(128, 256, 32), _rand(1, 256, 33)[0]
