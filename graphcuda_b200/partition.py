@@ -26,6 +26,8 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from .engine import _pad_cols, _padded_width
+
 
 # ---------------------------------------------------------------- partition arithmetic
 class RowPartition:
@@ -181,15 +183,22 @@ class DistGCNConvFunction(torch.autograd.Function):
         be = graph.backend
         fin, fout = W.shape
         transform_first = fout < fin  # the partitioned adjacency is symmetric by contract
+        width = fout
         if transform_first:
-            H = be.gemm(X, W, precision=precision)
-            Y = graph.aggregate(H, bias=bias, relu=bool(apply_relu), tag="f")
+            # odd output widths run zero-padded to a multiple of 4 (see engine._padded_width)
+            width = _padded_width(graph.n, fin, fout)
+            H = be.gemm(X, _pad_cols(W, width), precision=precision)
+            Y = graph.aggregate(H, bias=_pad_cols(bias, width) if bias is not None else None,
+                                relu=bool(apply_relu), tag="f")
+            if width != fout:
+                Y = Y[:, :fout]
             inter = None
         else:
             AX = graph.aggregate(X, gathered=X_gathered, tag="f")
             Y = be.gemm(AX, W, bias=bias, relu=bool(apply_relu), precision=precision)
             inter = AX
         ctx.graph = graph
+        ctx.width = width
         ctx.transform_first = transform_first
         ctx.apply_relu = bool(apply_relu)
         ctx.precision = precision
@@ -212,11 +221,13 @@ class DistGCNConvFunction(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[4]:
             db = graph.all_reduce_sum(G.sum(0))
         if ctx.transform_first:
-            S = graph.aggregate(G, tag="b")  # A^T G = A G (symmetric)
+            fout = W.size(1)
+            S = graph.aggregate(_pad_cols(G, ctx.width), tag="b")  # A^T G = A G (symmetric)
             if need_dW:
-                dW = graph.all_reduce_sum(be.gemm(X.t(), S, precision=ctx.precision))
+                dW = be.gemm(X.t(), S, precision=ctx.precision)[:, :fout].contiguous()
+                dW = graph.all_reduce_sum(dW)
             if need_dX:
-                dX = be.gemm(S, W.t(), precision=ctx.precision)
+                dX = be.gemm(S, _pad_cols(W, ctx.width).t(), precision=ctx.precision)
         else:
             AX = saved[3]
             if need_dW:

@@ -67,10 +67,13 @@ def _unique_undirected(u: torch.Tensor, v: torch.Tensor, n: int) -> torch.Tensor
 
 
 def rmat_edges(scale: int, n_nodes: int, n_edges: int, seed: int, device="cpu",
-               abcd=(0.57, 0.19, 0.19, 0.05)) -> torch.Tensor:
+               abcd=(0.57, 0.19, 0.19, 0.05), scramble: bool = True) -> torch.Tensor:
     """R-MAT on 2**scale ids; ids >= n_nodes, self-edges and duplicates are
     dropped; draws until n_edges distinct undirected edges exist and keeps a
-    seeded random subset of exactly that many."""
+    seeded random subset of exactly that many.  With `scramble` the vertex
+    labels are then permuted at random (as the Graph500 generator does), so
+    that the heavy vertices are not the low ids and contiguous row blocks of
+    the adjacency carry similar numbers of edges."""
     a, b, c, _ = abcd
     g = torch.Generator(device=device)
     g.manual_seed(seed)
@@ -100,7 +103,13 @@ def rmat_edges(scale: int, n_nodes: int, n_edges: int, seed: int, device="cpu",
     if keys.numel() > n_edges:
         perm = torch.randperm(keys.numel(), generator=g, device=device)[:n_edges]
         keys = keys[perm.sort().values]
-    return torch.stack([keys // n_nodes, keys % n_nodes])
+    u, v = keys // n_nodes, keys % n_nodes
+    if scramble:
+        relabel = torch.randperm(n_nodes, generator=g, device=device)
+        u, v = relabel[u], relabel[v]
+        keys = torch.sort(torch.minimum(u, v) * n_nodes + torch.maximum(u, v)).values
+        u, v = keys // n_nodes, keys % n_nodes
+    return torch.stack([u, v])
 
 
 def erdos_renyi_edges(n: int, p: float, seed: int, device="cpu") -> torch.Tensor:

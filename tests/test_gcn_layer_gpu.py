@@ -260,3 +260,29 @@ def test_input_layer_skips_dx(cuda):
     conv = graphcuda.GCNConv(20, 8).to(cuda)
     conv(X, A.to(cuda)).sum().backward()
     assert conv.weights.grad is not None and X.grad is None
+
+
+def test_odd_output_width_runs_padded(cuda):
+    """256 -> 47 on enough rows to take the zero-padded transform-first path
+    (aligned row pitches for the vector gathers and the tensor-core GEMMs)."""
+    import graphcuda
+    from graphcuda_b200 import engine, synth
+    n = 20_000
+    assert engine._padded_width(n, 256, 47) == 48
+    A = _graph(n, 10, seed=6)
+    X = synth.normal_features(n, 256, seed=8)
+    dY = synth.normal_features(n, 47, seed=9)
+    torch.manual_seed(21)
+    conv = graphcuda.GCNConv(256, 47, apply_relu=False).to(cuda)
+    W = conv.weights.detach().cpu()
+    Xr = X.clone().requires_grad_()
+    Wr = W.clone().requires_grad_()
+    Yr = A.mm(Xr).mm(Wr)
+    Yr.backward(dY)
+    Xg = X.to(cuda).requires_grad_()
+    Y = conv(Xg, A.to(cuda))
+    assert Y.shape == (n, 47)
+    Y.backward(dY.to(cuda))
+    assert O.rel_fro(Y, Yr) < TOL
+    assert O.rel_fro(Xg.grad, Xr.grad) < TOL
+    assert O.rel_fro(conv.weights.grad, Wr.grad) < TOL

@@ -146,3 +146,14 @@ def test_partitioned_model_matches_single_process(world, n, dims):
         for dw, conv in zip(dws, ref.convs):
             assert O.rel_fro(dw, conv.weights.grad) < 1e-5  # already summed over ranks
         assert abs(total - loss.item()) < 1e-5
+
+
+def test_width_padding_helpers():
+    from graphcuda_b200 import engine
+    assert engine._padded_width(2_449_029, 256, 47) == 48
+    assert engine._padded_width(2708, 16, 7) == 7          # small problems are not padded
+    assert engine._padded_width(2_449_029, 256, 256) == 256
+    W = torch.arange(6.0).reshape(2, 3)
+    P = engine._pad_cols(W, 4)
+    assert P.shape == (2, 4) and torch.equal(P[:, :3], W) and float(P[:, 3].abs().sum()) == 0.0
+    assert engine._pad_cols(W, 3) is W
