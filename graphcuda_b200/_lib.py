@@ -30,6 +30,8 @@ SIGNATURES = {
     "gc_spmm_scratch_bytes": (_size, [_i64, _i64]),
     "gc_spmm_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p, _i64,
                                _f32p, _void, _void, _size, _void]),
+    "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
+                                       _i64, _f32p, _void, _void]),
     "gc_gemm_workspace_bytes": (_size, [_int, _int, _i64, _i64, _i64, _int]),
     "gc_gemm_f32": (_int, [_int, _int, _i64, _i64, _i64, _f32p, _i64, _f32p, _i64, _f32p, _i64, _f32p, _int,
                            _f32p, _int, _void, _size, _void]),
@@ -48,6 +50,7 @@ SIGNATURES = {
 }
 
 # epilogue / precision constants of the header
+SPMM_STATIC_SCRATCH_BYTES = 8 << 20
 EPI_RELU = 1
 EPI_ACCUMULATE = 2
 EPI_TRANSPOSED_OUT = 4

@@ -20,6 +20,8 @@
 //     fp32 mask and an optional accumulate are fused into the store.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace {
 
 struct PlanHeader {
@@ -485,6 +487,62 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
     rc = gc::check_launch("gc_spmm_csr_f32 (finalize)");
   }
   return rc;
+}
+
+// ---------------------------------------------------------------- no-allocation variant
+// Scratch for gc_spmm_csr_f32_noalloc: part of the library image, so every
+// GPU that loads the library carries these bytes until the process exits.
+#define GC_SPMM_STATIC_SCRATCH_FLOATS (size_t(GC_SPMM_STATIC_SCRATCH_BYTES) / sizeof(float))
+static __device__ __align__(256) float g_static_scratch[GC_SPMM_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the CURRENT device.  In host code the
+// symbol's name is only a handle for the runtime, not a device address, so it
+// is translated with cudaGetSymbolAddress -- once per device, with that device
+// current -- and the translated pointer is what the kernels receive.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return gc::fail(GC_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+      return gc::fail(GC_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return GC_OK;
+}
+}  // namespace
+
+int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K,
+                            int64_t F, int64_t nnz, const float* H, int64_t ldH, const float* bias, int epilogue,
+                            float* Y, int64_t ldY, float* mask, const void* plan, void* stream) {
+  GC_REQUIRE(nnz >= 0, "gc_spmm_csr_f32_noalloc: negative nnz");
+  if (!plan)  // no long-row segments, hence no scratch at all
+    return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, nullptr, nullptr, 0,
+                           stream);
+  const size_t need = gc_spmm_scratch_bytes(nnz, F);
+  if (need > size_t(GC_SPMM_STATIC_SCRATCH_BYTES))
+    return gc::fail(GC_ERR_WORKSPACE,
+                    "gc_spmm_csr_f32_noalloc: nnz=%lld, F=%lld needs up to %zu bytes of scratch, the built-in "
+                    "buffer holds %zu; use gc_spmm_csr_f32 with caller-provided scratch",
+                    (long long)nnz, (long long)F, need, size_t(GC_SPMM_STATIC_SCRATCH_BYTES));
+  float* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != GC_OK) return rc;
+  // Every partial-sum row the finalize pass reads is fully written by the
+  // segment pass of the same call, so stale contents of the shared buffer are
+  // never observed and nothing has to be cleared.
+  return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, scratch,
+                         size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

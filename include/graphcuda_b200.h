@@ -85,6 +85,40 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
                     const void* plan, void* scratch, size_t scratch_bytes,
                     void* stream);
 
+/*
+ * The same aggregation for callers that must not allocate device memory.
+ *
+ * No counterpart in the reference (its SpMM wrapper cudaMallocs a workspace on
+ * every call, spmm_cusparse.cu:100-103).  Some hosts of this library cannot
+ * call cudaMalloc at the point where they need the product: a real-time or
+ * serving loop with a frozen memory budget, a plugin whose host application
+ * owns all device memory and hands out only the input and output buffers.  For them the long-row scratch lives in a
+ * fixed buffer inside the library image: GC_SPMM_STATIC_SCRATCH_BYTES bytes of
+ * device memory on every GPU that loads the library, held until the process
+ * exits.  The caller still passes the CSR arrays, H, Y (and the plan, which it
+ * built once into memory it owns).
+ *
+ *  - Limit: gc_spmm_scratch_bytes(nnz, F) must not exceed
+ *    GC_SPMM_STATIC_SCRATCH_BYTES; larger problems are refused with
+ *    GC_ERR_WORKSPACE and a message, never truncated.
+ *  - The first call on a device looks up the buffer's device address
+ *    (cudaGetSymbolAddress) with that device current; make that first call
+ *    outside any stream capture.  The device that owns `stream` must be the
+ *    current device.
+ *  - All calls on a device share the one buffer: two calls whose kernels can
+ *    overlap on the GPU (different streams, no dependency) race on it.
+ *    Serialise them or use gc_spmm_csr_f32 with separate scratch buffers.
+ *  - Nothing in the buffer has to be cleared between calls.
+ *  - Calls cudaMalloc / cudaFree / any allocating routine: never.
+ */
+#define GC_SPMM_STATIC_SCRATCH_BYTES (8u << 20)
+int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val,
+                            int64_t M, int64_t K, int64_t F, int64_t nnz,
+                            const float* H, int64_t ldH,
+                            const float* bias, int epilogue,
+                            float* Y, int64_t ldY, float* mask,
+                            const void* plan, void* stream);
+
 /* ---- dense GEMM --------------------------------------------------------- */
 
 /*
