@@ -25,13 +25,17 @@ SIGNATURES = {
     "gc_launch_count": (C.c_longlong, []),
     "gc_last_error": (C.c_char_p, []),
     "gc_status_string": (C.c_char_p, [_int]),
-    "gc_spmm_plan_bytes": (_size, [_i64]),
-    "gc_spmm_plan_build": (_int, [_i32p, _i64, _void, _size, _void]),
+    "gc_spmm_default_panel_cols": (_i64, [_i64, _i64]),
+    "gc_spmm_plan_workspace_bytes": (_size, [_i64, _i64]),
+    "gc_spmm_plan_count": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64p, _void, _size, _void]),
+    "gc_spmm_plan_bytes": (_size, [_i64, _i64]),
+    "gc_spmm_plan_build": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64, _i64, _i64, _void, _size, _void, _size,
+                                  _void]),
     "gc_spmm_scratch_bytes": (_size, [_i64, _i64]),
     "gc_spmm_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p, _i64,
-                               _f32p, _void, _void, _size, _void]),
-    "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
-                                       _i64, _f32p, _void, _void]),
+                               _f32p, _void, _i64, _i64, _void, _size, _void]),
+    "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
+                                       _i64, _f32p, _void, _i64, _i64, _i64, _void]),
     "gc_gemm_workspace_bytes": (_size, [_int, _int, _i64, _i64, _i64, _int]),
     "gc_gemm_f32": (_int, [_int, _int, _i64, _i64, _i64, _f32p, _i64, _f32p, _i64, _f32p, _i64, _f32p, _int,
                            _f32p, _int, _void, _size, _void]),

@@ -21,6 +21,15 @@ from . import _lib
 from .ops import _require, _stream, arena, EPI_RELU, EPI_ACCUMULATE
 
 
+class SpmmPlan:
+    """A built processing plan: device buffer and the counts it was built with."""
+
+    __slots__ = ("buf", "n_pieces", "n_slots", "n_cut", "panel_cols")
+
+    def __init__(self, buf, n_pieces, n_slots, n_cut, panel_cols):
+        self.buf, self.n_pieces, self.n_slots, self.n_cut, self.panel_cols = buf, n_pieces, n_slots, n_cut, panel_cols
+
+
 class CSRAdjacency:
     """int32 CSR on one device, with the SpMM plan and the symmetry verdict."""
 
@@ -38,19 +47,40 @@ class CSRAdjacency:
         self.nnz = int(col.numel())
         self.device = rowptr.device
         self._symmetric = symmetric
-        self.plan = None
-        if build_plan and self.shape[0] > 0:
-            self._build_plan()
+        self.use_plan = bool(build_plan)
+        self._plans = {}  # panel_cols -> SpmmPlan
 
-    def _build_plan(self) -> None:
+    def plan_for(self, F: int, panel_cols: Optional[int] = None):
+        """The processing plan for feature width F (built on first use and kept):
+        (plan buffer, n_pieces, n_slots, n_cut)."""
         L = _lib.lib()
-        M = self.shape[0]
-        nbytes = L.gc_spmm_plan_bytes(M)
-        plan = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
-        with torch.cuda.device(self.device):
-            st = L.gc_spmm_plan_build(self.rowptr.data_ptr(), M, plan.data_ptr(), nbytes, _stream(self.device))
-        _lib.check(st, "gc_spmm_plan_build")
-        self.plan = plan
+        M, K = self.shape
+        if panel_cols is None:
+            panel_cols = int(L.gc_spmm_default_panel_cols(K, max(F, 1)))
+        hit = self._plans.get(panel_cols)
+        if hit is not None:
+            return hit
+        dev = self.device
+        with torch.cuda.device(dev):
+            s = _stream(dev)
+            counts = torch.zeros(3, dtype=torch.int64, device=dev)
+            wsb = L.gc_spmm_plan_workspace_bytes(M, 0)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+            _lib.check(L.gc_spmm_plan_count(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols,
+                                            counts.data_ptr(), ws.data_ptr(), wsb, s), "gc_spmm_plan_count")
+            n_pieces, n_slots, n_cut = (int(x) for x in counts.tolist())  # the one host read of plan building
+            del ws
+            pbytes = L.gc_spmm_plan_bytes(n_pieces, n_cut)
+            plan = torch.empty(pbytes, dtype=torch.uint8, device=dev)
+            wsb = L.gc_spmm_plan_workspace_bytes(M, n_pieces)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+            _lib.check(L.gc_spmm_plan_build(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols,
+                                            n_pieces, n_slots, n_cut, plan.data_ptr(), pbytes, ws.data_ptr(), wsb,
+                                            s), "gc_spmm_plan_build")
+            torch.cuda.current_stream(dev).synchronize()  # ws is released below
+        entry = SpmmPlan(plan, n_pieces, n_slots, n_cut, panel_cols)
+        self._plans[panel_cols] = entry
+        return entry
 
     @property
     def symmetric(self) -> bool:
@@ -70,17 +100,15 @@ class CSRAdjacency:
                 self._symmetric = bool(out.item())
         return self._symmetric
 
-    def plan_counts(self):
-        """(long rows, segments) of the plan -- a device read, for tests and reports."""
-        if self.plan is None:
-            return (0, 0)
-        hdr = self.plan[:8].view(torch.int32).cpu()
-        return int(hdr[0]), int(hdr[1])
+    def plan_counts(self, F: int = 256, panel_cols: Optional[int] = None):
+        """(pieces, scratch slots, cut rows) of the plan for width F -- for tests and reports."""
+        p = self.plan_for(F, panel_cols)
+        return p.n_pieces, p.n_slots, p.n_cut
 
     # -- products -----------------------------------------------------------
     def matmul(self, H: torch.Tensor, *, bias: Optional[torch.Tensor] = None, relu: bool = False,
                want_mask: bool = False, accumulate_into: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None):
+               out: Optional[torch.Tensor] = None, panel_cols: Optional[int] = None):
         """Y = A @ H (+bias)(ReLU).  Returns Y or (Y, mask)."""
         _require(H.dim() == 2, "B must be 2D")
         _require(H.size(0) == self.shape[1], "A.cols must match B.rows")
@@ -107,16 +135,16 @@ class CSRAdjacency:
             return (out, mask) if want_mask else out
         L = _lib.lib()
         with torch.cuda.device(dev):
-            plan_ptr = self.plan.data_ptr() if self.plan is not None else None
+            plan = self.plan_for(F, panel_cols) if self.use_plan else None
             scratch = None
-            sbytes = 0
-            if self.plan is not None:
-                sbytes = L.gc_spmm_scratch_bytes(self.nnz, F)
-                scratch = arena.get("spmm", sbytes, dev)
+            if plan is not None and plan.n_cut > 0:
+                scratch = arena.get("spmm", L.gc_spmm_scratch_bytes(plan.n_slots, F), dev)
             ldh = H.stride(0) if H.size(0) > 1 else max(F, 1)
             st = L.gc_spmm_csr_f32(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
                                    H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None, epi,
-                                   out.data_ptr(), F, mask.data_ptr() if mask is not None else None, plan_ptr,
+                                   out.data_ptr(), F, mask.data_ptr() if mask is not None else None,
+                                   plan.buf.data_ptr() if plan is not None else None,
+                                   plan.n_pieces if plan is not None else 0, plan.n_cut if plan is not None else 0,
                                    scratch.data_ptr() if scratch is not None else None,
                                    scratch.numel() if scratch is not None else 0, _stream(dev))
         _lib.check(st, "gc_spmm_csr_f32")

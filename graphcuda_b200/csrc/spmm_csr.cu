@@ -4,35 +4,71 @@
 // (src/graphcuda/cuda/spmm_cusparse.cu:3-126) on the GCN path
 // (src/graphcuda/cuda/gcn.cu:12,40,49).
 //
-// HBM/L2-bound gather.  Layout and schedule:
-//   * a row of Y is produced by a "group" of GROUP lanes (GROUP = 2..32, the
-//     smallest power of two that covers the feature width with 128-bit
-//     loads), so narrow feature widths keep all 32 lanes of a warp busy on
-//     several rows at once;
-//   * the group's lanes fetch GROUP (col,val) pairs with one coalesced load
-//     and broadcast them with shuffles; the H row of each non-zero is read
-//     with 128-bit loads, four non-zeros in flight per lane;
-//   * rows longer than GC_SPMM_LONG_ROW are cut into GC_SPMM_SEGMENT-sized
-//     segments, one CTA per segment, partial sums to scratch, then a
-//     finalize pass adds the segments in order -- no atomics anywhere, so the
-//     result is bit-reproducible run to run;
-//   * bias, ReLU (as y * (y > 0), the reference's formula, gcn.cu:19-20), the
-//     fp32 mask and an optional accumulate are fused into the store.
+// The product is a gather: every non-zero (i, j) reads row j of H.  On
+// power-law graphs most of that traffic is not compulsory -- H is far larger
+// than the 126 MB L2 and the heavy rows pull in rows of H from everywhere.
+// The schedule therefore works on "pieces" (a contiguous run of non-zeros of
+// one row) listed by a plan that is built once per CSR structure:
+//   * rows with more than GC_SPMM_PANEL_MIN_ROW non-zeros are cut at column
+//     panel boundaries (panel = a range of columns whose rows of H fit the
+//     L2 together); pieces are processed panel by panel, so the whole GPU
+//     gathers from one L2-resident slab of H at a time;
+//   * any piece longer than GC_SPMM_SEGMENT is cut further, so a hub row is
+//     spread over many warps;
+//   * pieces of cut rows write partial sums to scratch; a finalize pass adds
+//     a row's partials in piece order and applies the epilogue -- no atomics
+//     anywhere, results are bit-reproducible run to run;
+//   * uncut rows are processed after the panels, longest first, and write Y
+//     directly with the fused epilogue;
+//   * within a phase pieces are sorted by length, so the sub-warp groups of a
+//     warp carry similar work.
+// A piece is handled by a group of GROUP lanes (2..32): the lanes fetch GROUP
+// (col, val) pairs with one coalesced load (the next batch is prefetched),
+// broadcast them with shuffles and gather the H rows with 128-bit loads,
+// U non-zeros x NACC vectors in flight per lane.
+// Bias, ReLU (as y * (y > 0), the reference's formula, gcn.cu:19-20), the fp32
+// mask and an optional accumulate are fused into the store.
 #include "common.cuh"
 
+#include <algorithm>
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 #include <mutex>
 
 namespace {
 
 struct PlanHeader {
-  int32_t n_long;
-  int32_t n_seg;
+  int32_t magic;
+  int32_t M;
+  int32_t n_pieces;  // entries of the piece list
+  int32_t n_slots;   // partial-sum rows in scratch (pieces of cut rows)
+  int32_t n_cut;     // rows that were cut
+  int32_t panel_cols;
   int32_t pad[2];
 };
+constexpr int32_t kPlanMagic = 0x47435032;  // "GCP2"
 
-__host__ __device__ inline size_t plan_long_rows_offset() { return sizeof(PlanHeader); }
-__host__ __device__ inline size_t plan_seg_off_offset(int64_t M) {
-  return sizeof(PlanHeader) + ((size_t(M) * 4 + 15) & ~size_t(15));
+inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
+
+// Plan memory: header | piece_start[n] | piece_len[n] | piece_target[n] |
+//              cut_row[c] | cut_slot0[c] | cut_nslots[c]
+struct PlanView {
+  PlanHeader* hdr;
+  int32_t *start, *len, *target, *cut_row, *cut_slot0, *cut_nslots;
+};
+inline PlanView plan_view(void* plan, int64_t n_pieces, int64_t n_cut) {
+  char* p = static_cast<char*>(plan);
+  PlanView v;
+  v.hdr = reinterpret_cast<PlanHeader*>(p);
+  size_t off = sizeof(PlanHeader);
+  const size_t np = align16(size_t(n_pieces) * 4), nc = align16(size_t(n_cut) * 4);
+  v.start = reinterpret_cast<int32_t*>(p + off); off += np;
+  v.len = reinterpret_cast<int32_t*>(p + off); off += np;
+  v.target = reinterpret_cast<int32_t*>(p + off); off += np;
+  v.cut_row = reinterpret_cast<int32_t*>(p + off); off += nc;
+  v.cut_slot0 = reinterpret_cast<int32_t*>(p + off); off += nc;
+  v.cut_nslots = reinterpret_cast<int32_t*>(p + off);
+  return v;
 }
 
 // ---------------------------------------------------------------- epilogue
@@ -96,55 +132,77 @@ __device__ __forceinline__ void finish_store(typename Vec<VW>::T acc, float* yro
   V::store(yrow + f, acc);
 }
 
-// ---------------------------------------------------------------- row kernel
-// One group of GROUP lanes per row; NACC vectors of VW floats per lane cover
+// ---------------------------------------------------------------- piece kernel
+// One group of GROUP lanes per piece; NACC vectors of VW floats per lane cover
 // GROUP*NACC*VW feature columns per pass; wider F loops over passes.
-template <int GROUP, int NACC, int VW>
+// PLANNED: pieces come from the plan (target >= 0: row of Y with the
+// epilogue; target < 0: scratch row ~target, raw sums); otherwise piece v is
+// row v of the matrix.
+template <int GROUP, int NACC, int VW, int U, bool PLANNED>
 __global__ void __launch_bounds__(256)
-spmm_rows_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col,
-                 const float* __restrict__ val, int M, int F, const float* __restrict__ H, int64_t ldH,
-                 float* __restrict__ Y, int64_t ldY, Epilogue ep, int skip_long) {
+spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col,
+                   const float* __restrict__ val, int n_pieces, const int32_t* __restrict__ p_start,
+                   const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
+                   const float* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
+                   float* __restrict__ scratch, int64_t ldS, int slot_capacity, Epilogue ep) {
   using V = Vec<VW>;
-  constexpr int ROWS_PER_CTA = 256 / GROUP;
+  constexpr int PIECES_PER_CTA = 256 / GROUP;
   constexpr int PASS = GROUP * NACC * VW;
-  constexpr int U = GROUP < 4 ? GROUP : 4;
+  static_assert(U <= GROUP, "a round cannot be wider than a batch");
   const int lane_g = threadIdx.x % GROUP;
-  const int row = blockIdx.x * ROWS_PER_CTA + threadIdx.x / GROUP;
-  if (row >= M) return;
+  const int v = blockIdx.x * PIECES_PER_CTA + threadIdx.x / GROUP;
+  if (v >= n_pieces) return;
   const unsigned gmask = (GROUP == 32) ? 0xffffffffu
                                        : (((1u << GROUP) - 1u) << ((threadIdx.x % 32) / GROUP * GROUP));
-  const int start = __ldg(rowptr + row);
-  const int end = __ldg(rowptr + row + 1);
-  if (skip_long && (end - start) > GC_SPMM_LONG_ROW) return;
-  float* yrow = Y + int64_t(row) * ldY;
-  float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
+  int start, end, target;
+  if (PLANNED) {
+    start = __ldg(p_start + v);
+    end = start + __ldg(p_len + v);
+    target = __ldg(p_target + v);
+  } else {
+    start = __ldg(rowptr + v);
+    end = __ldg(rowptr + v + 1);
+    target = v;
+  }
+  const bool direct = target >= 0;
+  if (!direct && (~target) >= slot_capacity) return;  // never write past the caller's scratch
+  float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
+  float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
+  Epilogue my_ep = ep;
+  if (!direct) my_ep = Epilogue{nullptr, nullptr, 0, 0};
 
   for (int f0 = 0; f0 < F; f0 += PASS) {
     typename V::T acc[NACC];
-#pragma unroll
-    for (int a = 0; a < NACC; ++a) acc[a] = V::zero();
     bool live[NACC];
 #pragma unroll
-    for (int a = 0; a < NACC; ++a) live[a] = (f0 + (a * GROUP + lane_g) * VW) < F;
-
+    for (int a = 0; a < NACC; ++a) {
+      acc[a] = V::zero();
+      live[a] = (f0 + (a * GROUP + lane_g) * VW) < F;
+    }
+    int c_next = 0;
+    float w_next = 0.f;
+    if (start + lane_g < end) {
+      c_next = __ldg(col + start + lane_g);
+      w_next = __ldg(val + start + lane_g);
+    }
     for (int base = start; base < end; base += GROUP) {
-      const int e = base + lane_g;
-      int c = 0;
-      float v = 0.f;
-      if (e < end) {
-        c = __ldg(col + e);
-        v = __ldg(val + e);
+      const int c = c_next;
+      const float w = w_next;
+      const int e2 = base + GROUP + lane_g;  // prefetch the next batch of (col, val)
+      if (e2 < end) {
+        c_next = __ldg(col + e2);
+        w_next = __ldg(val + e2);
       }
       const int cnt = min(GROUP, end - base);
-      // U gathers in flight per lane; entries past the end of the row are
-      // never loaded (a 0 * Inf would poison the sum).
+      // U gathers in flight per lane and accumulator; entries past the end of
+      // the piece are never loaded (a 0 * Inf would poison the sum).
       for (int j = 0; j < cnt; j += U) {
         int cj[U];
-        float vj[U];
+        float wj[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          cj[u] = __shfl_sync(gmask, c, j + u, GROUP);
-          vj[u] = __shfl_sync(gmask, v, j + u, GROUP);
+          cj[u] = __shfl_sync(gmask, c, (j + u) % GROUP, GROUP);
+          wj[u] = __shfl_sync(gmask, w, (j + u) % GROUP, GROUP);
         }
         typename V::T h[U][NACC];
 #pragma unroll
@@ -158,251 +216,271 @@ spmm_rows_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
-          for (int a = 0; a < NACC; ++a) V::fma(acc[a], (j + u) < cnt ? vj[u] : 0.f, h[u][a]);
+          for (int a = 0; a < NACC; ++a) V::fma(acc[a], (j + u) < cnt ? wj[u] : 0.f, h[u][a]);
       }
     }
 #pragma unroll
     for (int a = 0; a < NACC; ++a)
-      if (live[a]) finish_store<VW>(acc[a], yrow, mrow, f0 + (a * GROUP + lane_g) * VW, ep);
+      if (live[a]) finish_store<VW>(acc[a], yrow, mrow, f0 + (a * GROUP + lane_g) * VW, my_ep);
   }
 }
 
-// ---------------------------------------------------------------- long rows
-// One CTA (8 warps) per segment of a long row; warps interleave 32-entry
-// batches, then their partial vectors are added in warp order through shared
-// memory and written to scratch[segment][F].
-template <int NACC, int VW>
+// One warp per cut row: adds that row's partial sums in slot order, then the fused store.
 __global__ void __launch_bounds__(256)
-spmm_segments_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col,
-                     const float* __restrict__ val, int F, const float* __restrict__ H, int64_t ldH,
-                     const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ long_rows,
-                     const int32_t* __restrict__ seg_off, float* __restrict__ scratch, int64_t ldS,
-                     int seg_capacity) {
-  using V = Vec<VW>;
-  constexpr int PASS = 32 * NACC * VW;
-  __shared__ __align__(16) float red[8][PASS];
-  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-  // never write past the caller's scratch, whatever the plan says
-  const int n_seg = min(hdr->n_seg, seg_capacity), n_long = hdr->n_long;
-  for (int seg = blockIdx.x; seg < n_seg; seg += gridDim.x) {
-    // largest i with seg_off[i] <= seg
-    int lo = 0, hi = n_long;
-    while (hi - lo > 1) {
-      int mid = (lo + hi) >> 1;
-      if (__ldg(seg_off + mid) <= seg) lo = mid; else hi = mid;
-    }
-    const int row = __ldg(long_rows + lo);
-    const int rstart = __ldg(rowptr + row), rend = __ldg(rowptr + row + 1);
-    const int start = rstart + (seg - __ldg(seg_off + lo)) * GC_SPMM_SEGMENT;
-    const int end = min(start + GC_SPMM_SEGMENT, rend);
-    for (int f0 = 0; f0 < F; f0 += PASS) {
-      typename V::T acc[NACC];
-      bool live[NACC];
-#pragma unroll
-      for (int a = 0; a < NACC; ++a) {
-        acc[a] = V::zero();
-        live[a] = (f0 + (a * 32 + lane) * VW) < F;
-      }
-      for (int base = start + warp * 32; base < end; base += 256) {
-        const int e = base + lane;
-        int c = 0;
-        float v = 0.f;
-        if (e < end) {
-          c = __ldg(col + e);
-          v = __ldg(val + e);
-        }
-        const int cnt = min(32, end - base);
-        for (int j = 0; j < cnt; j += 4) {
-          int cj[4];
-          float vj[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            cj[u] = __shfl_sync(0xffffffffu, c, (j + u) & 31);
-            vj[u] = __shfl_sync(0xffffffffu, v, (j + u) & 31);
-          }
-          typename V::T h[4][NACC];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float* hp = H + int64_t(cj[u]) * ldH + f0;
-            const bool valid = (j + u) < cnt;
-#pragma unroll
-            for (int a = 0; a < NACC; ++a)
-              h[u][a] = (live[a] && valid) ? V::load(hp + (a * 32 + lane) * VW) : V::zero();
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-#pragma unroll
-            for (int a = 0; a < NACC; ++a) V::fma(acc[a], (j + u) < cnt ? vj[u] : 0.f, h[u][a]);
-        }
-      }
-#pragma unroll
-      for (int a = 0; a < NACC; ++a) V::store(&red[warp][(a * 32 + lane) * VW], acc[a]);
-      __syncthreads();
-      for (int i = threadIdx.x; i < PASS; i += 256) {
-        if (f0 + i < F) {
-          float s = red[0][i];
-#pragma unroll
-          for (int w = 1; w < 8; ++w) s += red[w][i];
-          scratch[int64_t(seg) * ldS + f0 + i] = s;
-        }
-      }
-      __syncthreads();
-    }
-  }
-}
-
-// One warp per long row: adds that row's segments in order, then the fused store.
-__global__ void __launch_bounds__(256)
-spmm_finalize_kernel(int F, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ long_rows,
-                     const int32_t* __restrict__ seg_off, const float* __restrict__ scratch, int64_t ldS,
-                     float* __restrict__ Y, int64_t ldY, Epilogue ep) {
+spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, const int32_t* __restrict__ cut_slot0,
+                     const int32_t* __restrict__ cut_nslots, const float* __restrict__ scratch, int64_t ldS,
+                     int slot_capacity, float* __restrict__ Y, int64_t ldY, Epilogue ep) {
   const int lane = threadIdx.x % 32;
-  const int n_long = hdr->n_long;
   const int warps = gridDim.x * 8;
-  for (int i = blockIdx.x * 8 + threadIdx.x / 32; i < n_long; i += warps) {
-    const int row = __ldg(long_rows + i);
-    const int s0 = __ldg(seg_off + i), s1 = __ldg(seg_off + i + 1);
+  for (int i = blockIdx.x * 8 + threadIdx.x / 32; i < n_cut; i += warps) {
+    const int row = __ldg(cut_row + i);
+    const int s0 = __ldg(cut_slot0 + i);
+    const int s1 = min(s0 + __ldg(cut_nslots + i), slot_capacity);
     float* yrow = Y + int64_t(row) * ldY;
     float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
     for (int f = lane; f < F; f += 32) {
       float s = 0.f;
-      for (int sgi = s0; sgi < s1; ++sgi) s += scratch[int64_t(sgi) * ldS + f];
+      for (int sl = s0; sl < s1; ++sl) s += scratch[int64_t(sl) * ldS + f];
       finish_store<1>(s, yrow, mrow, f, ep);
     }
   }
 }
 
-// ---------------------------------------------------------------- plan
-__global__ void plan_collect_kernel(const int32_t* __restrict__ rowptr, int M, PlanHeader* hdr,
-                                    int32_t* __restrict__ flags) {
-  int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row < M) flags[row] = (__ldg(rowptr + row + 1) - __ldg(rowptr + row)) > GC_SPMM_LONG_ROW ? 1 : 0;
+// ---------------------------------------------------------------- plan construction
+__device__ __forceinline__ int lower_bound_col(const int32_t* __restrict__ col, int lo, int hi, int key) {
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(col + mid) < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
 }
 
-// Single CTA: ordered compaction of the long rows (ascending row id) and the
-// running segment count.  The per-row flags live in the seg_off area of the
-// plan (M+1 ints); pass 1 consumes all of them before pass 2 overwrites the
-// first n_long+1 entries with the segment offsets.
-__global__ void __launch_bounds__(1024)
-plan_scan_kernel(const int32_t* __restrict__ rowptr, int M, PlanHeader* hdr, int32_t* long_rows,
-                 int32_t* flags_then_seg_off) {
-  __shared__ int warp_sums[32];
-  __shared__ int carry_s;
-  const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
-  if (tid == 0) carry_s = 0;
-  __syncthreads();
-  // pass 1: compact long rows in ascending order
-  for (int base = 0; base < M; base += 1024) {
-    const int row = base + tid;
-    const int f = (row < M) ? flags_then_seg_off[row] : 0;
-    int x = f;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+__device__ __forceinline__ int pieces_of(int cnt) { return (cnt + GC_SPMM_SEGMENT - 1) / GC_SPMM_SEGMENT; }
+
+// Per row: how many pieces it contributes and whether it is cut.
+__global__ void __launch_bounds__(256)
+plan_count_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col, int M, int K, int panel_cols,
+                  int32_t* __restrict__ rows_pieces, int32_t* __restrict__ rows_cut,
+                  int32_t* __restrict__ rows_slots) {
+  const int r = blockIdx.x * 256 + threadIdx.x;
+  if (r >= M) return;
+  const int s = __ldg(rowptr + r), e = __ldg(rowptr + r + 1), d = e - s;
+  const int n_panels = (K + panel_cols - 1) / panel_cols;
+  int pieces;
+  if (d > GC_SPMM_PANEL_MIN_ROW && n_panels > 1) {
+    pieces = 0;
+    int lo = s;
+    for (int p = 0; p < n_panels && lo < e; ++p) {
+      const int hi = (p + 1 == n_panels) ? e : lower_bound_col(col, lo, e, (p + 1) * panel_cols);
+      pieces += pieces_of(hi - lo);
+      lo = hi;
     }
-    if (lane == 31) warp_sums[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_sums[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int y = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += y;
-      }
-      warp_sums[lane] = w;
-    }
-    __syncthreads();
-    const int carry = carry_s;
-    const int incl = x + (warp ? warp_sums[warp - 1] : 0);
-    if (f) long_rows[carry + incl - 1] = row;
-    __syncthreads();
-    if (tid == 1023) carry_s = carry + incl;
-    __syncthreads();
+  } else {
+    pieces = max(1, pieces_of(d));
   }
-  const int n_long = carry_s;
-  __syncthreads();
-  // pass 2: exclusive scan of segments per long row
-  if (tid == 0) carry_s = 0;
-  __syncthreads();
-  for (int base = 0; base < n_long; base += 1024) {
-    const int i = base + tid;
-    int nseg = 0;
-    if (i < n_long) {
-      const int r = long_rows[i];
-      const int deg = __ldg(rowptr + r + 1) - __ldg(rowptr + r);
-      nseg = (deg + GC_SPMM_SEGMENT - 1) / GC_SPMM_SEGMENT;
-    }
-    int x = nseg;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
-    }
-    if (lane == 31) warp_sums[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_sums[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int y = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += y;
-      }
-      warp_sums[lane] = w;
-    }
-    __syncthreads();
-    const int carry = carry_s;
-    const int incl = x + (warp ? warp_sums[warp - 1] : 0);
-    if (i < n_long) flags_then_seg_off[i] = carry + incl - nseg;
-    __syncthreads();
-    if (tid == 1023) carry_s = carry + incl;
-    __syncthreads();
+  rows_pieces[r] = pieces;
+  rows_cut[r] = pieces > 1 ? 1 : 0;
+  rows_slots[r] = pieces > 1 ? pieces : 0;
+}
+
+__global__ void plan_totals_kernel(const int32_t* __restrict__ rows_pieces, const int32_t* __restrict__ rows_cut,
+                                   const int32_t* __restrict__ rows_slots, const int32_t* __restrict__ piece_base,
+                                   const int32_t* __restrict__ cut_base, const int32_t* __restrict__ slot_base,
+                                   int M, int64_t* __restrict__ counts) {
+  if (M == 0) { counts[0] = counts[1] = counts[2] = 0; return; }
+  const int l = M - 1;
+  counts[0] = int64_t(piece_base[l]) + rows_pieces[l];  // pieces
+  counts[1] = int64_t(slot_base[l]) + rows_slots[l];    // scratch slots
+  counts[2] = int64_t(cut_base[l]) + rows_cut[l];       // cut rows
+}
+
+// Emits the pieces of every row with a sort key (phase << 32 | ~length):
+// phase = panel index for pieces of panel-cut rows, 0 for rows cut by length
+// only, n_panels for uncut rows (they run after all panels).
+__global__ void __launch_bounds__(256)
+plan_emit_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col, int M, int K, int panel_cols,
+                 const int32_t* __restrict__ rows_cut, const int32_t* __restrict__ piece_base,
+                 const int32_t* __restrict__ cut_base, const int32_t* __restrict__ slot_base,
+                 const int32_t* __restrict__ rows_pieces, uint64_t* __restrict__ keys, int32_t* __restrict__ ids,
+                 int32_t* __restrict__ u_start, int32_t* __restrict__ u_len, int32_t* __restrict__ u_target,
+                 int32_t* __restrict__ cut_row, int32_t* __restrict__ cut_slot0, int32_t* __restrict__ cut_nslots) {
+  const int r = blockIdx.x * 256 + threadIdx.x;
+  if (r >= M) return;
+  const int s = __ldg(rowptr + r), e = __ldg(rowptr + r + 1), d = e - s;
+  const int n_panels = (K + panel_cols - 1) / panel_cols;
+  int out = piece_base[r];
+  if (!rows_cut[r]) {
+    u_start[out] = s;
+    u_len[out] = d;
+    u_target[out] = r;
+    keys[out] = (uint64_t(uint32_t(n_panels)) << 32) | uint64_t(0xFFFFFFFFu - uint32_t(d));
+    ids[out] = out;
+    return;
   }
-  if (tid == 0) {
-    flags_then_seg_off[n_long] = carry_s;
-    hdr->n_long = n_long;
-    hdr->n_seg = carry_s;
-    hdr->pad[0] = hdr->pad[1] = 0;
+  int slot = slot_base[r];
+  const int ci = cut_base[r];
+  cut_row[ci] = r;
+  cut_slot0[ci] = slot;
+  cut_nslots[ci] = rows_pieces[r];
+  const bool by_panel = d > GC_SPMM_PANEL_MIN_ROW && n_panels > 1;
+  int lo = s;
+  for (int p = 0; p < (by_panel ? n_panels : 1) && lo < e; ++p) {
+    const int hi = (!by_panel || p + 1 == n_panels) ? e : lower_bound_col(col, lo, e, (p + 1) * panel_cols);
+    for (int q = lo; q < hi; q += GC_SPMM_SEGMENT) {
+      const int len = min(GC_SPMM_SEGMENT, hi - q);
+      u_start[out] = q;
+      u_len[out] = len;
+      u_target[out] = ~slot;
+      keys[out] = (uint64_t(uint32_t(by_panel ? p : 0)) << 32) | uint64_t(0xFFFFFFFFu - uint32_t(len));
+      ids[out] = out;
+      ++out;
+      ++slot;
+    }
+    lo = hi;
   }
+}
+
+__global__ void __launch_bounds__(256)
+plan_gather_kernel(const int32_t* __restrict__ ids_sorted, int n, const int32_t* __restrict__ u_start,
+                   const int32_t* __restrict__ u_len, const int32_t* __restrict__ u_target,
+                   int32_t* __restrict__ start, int32_t* __restrict__ len, int32_t* __restrict__ target) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const int j = ids_sorted[i];
+  start[i] = u_start[j];
+  len[i] = u_len[j];
+  target[i] = u_target[j];
+}
+
+__global__ void plan_header_kernel(PlanHeader* hdr, int M, int n_pieces, int n_slots, int n_cut, int panel_cols) {
+  hdr->magic = kPlanMagic;
+  hdr->M = M;
+  hdr->n_pieces = n_pieces;
+  hdr->n_slots = n_slots;
+  hdr->n_cut = n_cut;
+  hdr->panel_cols = panel_cols;
+  hdr->pad[0] = hdr->pad[1] = 0;
+}
+
+// Workspace carve-up shared by the count and build steps.
+struct PlanWs {
+  int32_t *rows_pieces, *rows_cut, *rows_slots, *piece_base, *cut_base, *slot_base;
+  uint64_t *keys, *keys_alt;
+  int32_t *ids, *ids_alt, *u_start, *u_len, *u_target;
+  void* cub;
+  size_t cub_bytes;
+  size_t total;
+};
+
+// Temporary storage for the CUB scan / sort.  Sized by formula rather than by
+// querying CUB, so the answer is the same on a machine without a GPU: the
+// one-sweep radix sort and the decoupled look-back scan need a few bytes per
+// 1000 items plus fixed histograms.
+size_t cub_temp_bytes(int64_t M, int64_t n_pieces) {
+  return (size_t(4) << 20) + size_t(std::max<int64_t>(M, n_pieces)) / 4;
+}
+
+PlanWs carve(void* ws, int64_t M, int64_t n_pieces) {
+  PlanWs w{};
+  char* p = static_cast<char*>(ws);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char* q = p ? p + off : nullptr;
+    off += (bytes + 255) & ~size_t(255);
+    return q;
+  };
+  const size_t m4 = size_t(std::max<int64_t>(M, 1)) * 4, n4 = size_t(std::max<int64_t>(n_pieces, 1)) * 4;
+  w.rows_pieces = reinterpret_cast<int32_t*>(take(m4));
+  w.rows_cut = reinterpret_cast<int32_t*>(take(m4));
+  w.rows_slots = reinterpret_cast<int32_t*>(take(m4));
+  w.piece_base = reinterpret_cast<int32_t*>(take(m4));
+  w.cut_base = reinterpret_cast<int32_t*>(take(m4));
+  w.slot_base = reinterpret_cast<int32_t*>(take(m4));
+  w.keys = reinterpret_cast<uint64_t*>(take(n4 * 2));
+  w.keys_alt = reinterpret_cast<uint64_t*>(take(n4 * 2));
+  w.ids = reinterpret_cast<int32_t*>(take(n4));
+  w.ids_alt = reinterpret_cast<int32_t*>(take(n4));
+  w.u_start = reinterpret_cast<int32_t*>(take(n4));
+  w.u_len = reinterpret_cast<int32_t*>(take(n4));
+  w.u_target = reinterpret_cast<int32_t*>(take(n4));
+  w.cub_bytes = cub_temp_bytes(M, n_pieces);
+  w.cub = take(w.cub_bytes);
+  w.total = off;
+  return w;
+}
+
+int exclusive_scan(const PlanWs& w, const int32_t* in, int32_t* out, int n, cudaStream_t st) {
+  size_t need = 0;
+  cudaError_t e = cub::DeviceScan::ExclusiveSum(nullptr, need, in, out, n, st);
+  if (e == cudaSuccess && need > w.cub_bytes)
+    return gc::fail(GC_ERR_WORKSPACE, "spmm plan: scan needs %zu bytes of temporary storage, have %zu", need,
+                    w.cub_bytes);
+  size_t b = w.cub_bytes;
+  if (e == cudaSuccess) e = cub::DeviceScan::ExclusiveSum(w.cub, b, in, out, n, st);
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "spmm plan: scan: %s", cudaGetErrorString(e));
+  gc::count_launches(1);
+  return GC_OK;
+}
+
+int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int panel_cols, const PlanWs& w,
+               cudaStream_t st) {
+  const unsigned g = unsigned((M + 255) / 256);
+  plan_count_kernel<<<g, 256, 0, st>>>(rowptr, col, M, K, panel_cols, w.rows_pieces, w.rows_cut, w.rows_slots);
+  int rc = gc::check_launch("spmm plan: count");
+  if (rc == GC_OK) rc = exclusive_scan(w, w.rows_pieces, w.piece_base, M, st);
+  if (rc == GC_OK) rc = exclusive_scan(w, w.rows_cut, w.cut_base, M, st);
+  if (rc == GC_OK) rc = exclusive_scan(w, w.rows_slots, w.slot_base, M, st);
+  return rc;
 }
 
 // ---------------------------------------------------------------- dispatch
-template <int GROUP, int NACC, int VW>
-void launch_rows(const int32_t* rowptr, const int32_t* col, const float* val, int M, int F, const float* H,
-                 int64_t ldH, float* Y, int64_t ldY, const Epilogue& ep, int skip_long, cudaStream_t st) {
-  constexpr int ROWS_PER_CTA = 256 / GROUP;
-  const unsigned grid = unsigned((M + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
-  spmm_rows_kernel<GROUP, NACC, VW><<<grid, 256, 0, st>>>(rowptr, col, val, M, F, H, ldH, Y, ldY, ep, skip_long);
-}
-
-template <int VW>
-void dispatch_rows(const int32_t* rowptr, const int32_t* col, const float* val, int M, int F, const float* H,
-                   int64_t ldH, float* Y, int64_t ldY, const Epilogue& ep, int skip_long, cudaStream_t st) {
-  const int units = (F + VW - 1) / VW;  // vectors per row
-#define GC_ROWS(G, A) launch_rows<G, A, VW>(rowptr, col, val, M, F, H, ldH, Y, ldY, ep, skip_long, st)
-  if (units <= 2) GC_ROWS(2, 1);
-  else if (units <= 4) GC_ROWS(4, 1);
-  else if (units <= 8) GC_ROWS(8, 1);
-  else if (units <= 16) GC_ROWS(16, 1);
-  else if (units <= 32) GC_ROWS(32, 1);
-  else if (units <= 64) GC_ROWS(32, 2);
-  else GC_ROWS(32, 4);
-#undef GC_ROWS
-}
-
-template <int VW>
-void dispatch_segments(const int32_t* rowptr, const int32_t* col, const float* val, int F, const float* H,
-                       int64_t ldH, const PlanHeader* hdr, const int32_t* long_rows, const int32_t* seg_off,
-                       float* scratch, int64_t ldS, int cap, cudaStream_t st) {
-  const int units = (F + VW - 1) / VW;
-  const unsigned grid = gc::kNumSMs * 8;
-  if (units <= 32)
-    spmm_segments_kernel<1, VW><<<grid, 256, 0, st>>>(rowptr, col, val, F, H, ldH, hdr, long_rows, seg_off, scratch, ldS, cap);
-  else if (units <= 64)
-    spmm_segments_kernel<2, VW><<<grid, 256, 0, st>>>(rowptr, col, val, F, H, ldH, hdr, long_rows, seg_off, scratch, ldS, cap);
+template <int GROUP, int NACC, int VW, int U>
+void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
+                   const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
+                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                   cudaStream_t st) {
+  constexpr int PER_CTA = 256 / GROUP;
+  const unsigned grid = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
+  if (planned)
+    spmm_pieces_kernel<GROUP, NACC, VW, U, true><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H,
+                                                                       ldH, Y, ldY, scratch, ldS, cap, ep);
   else
-    spmm_segments_kernel<4, VW><<<grid, 256, 0, st>>>(rowptr, col, val, F, H, ldH, hdr, long_rows, seg_off, scratch, ldS, cap);
+    spmm_pieces_kernel<GROUP, NACC, VW, U, false><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F,
+                                                                        H, ldH, Y, ldY, scratch, ldS, cap, ep);
 }
+
+#define GC_PIECES(G, A, VWID, UU)                                                                                 \
+  launch_pieces<G, A, VWID, UU>(planned, rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, \
+                                cap, ep, st)
+
+// GROUP x NACC 128-bit vectors cover a row of H; small groups keep several
+// pieces in flight per warp and four accumulators per lane amortise the
+// (col, val) broadcast.
+void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
+                   const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
+                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                   cudaStream_t st) {
+  const int units = F / 4;  // 128-bit vectors per row
+  if (units <= 2) GC_PIECES(2, 1, 4, 2);
+  else if (units <= 4) GC_PIECES(2, 2, 4, 2);
+  else if (units <= 8) GC_PIECES(2, 4, 4, 2);
+  else if (units <= 16) GC_PIECES(4, 4, 4, 4);
+  else if (units <= 32) GC_PIECES(8, 4, 4, 4);
+  else if (units <= 64) GC_PIECES(16, 4, 4, 4);
+  else GC_PIECES(32, 4, 4, 2);
+}
+
+void dispatch_scalar(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
+                     const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
+                     float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                     cudaStream_t st) {
+  if (F <= 8) GC_PIECES(8, 1, 1, 4);
+  else if (F <= 16) GC_PIECES(16, 1, 1, 4);
+  else if (F <= 32) GC_PIECES(32, 1, 1, 4);
+  else if (F <= 64) GC_PIECES(32, 2, 1, 4);
+  else GC_PIECES(32, 4, 1, 4);
+}
+#undef GC_PIECES
 
 inline int64_t scratch_ld(int64_t F) { return (F + 3) & ~int64_t(3); }
 
@@ -410,80 +488,146 @@ inline int64_t scratch_ld(int64_t F) { return (F + 3) & ~int64_t(3); }
 
 extern "C" {
 
-size_t gc_spmm_plan_bytes(int64_t M) {
-  if (M < 0) return 0;
-  return plan_seg_off_offset(M) + ((size_t(M + 1) * 4 + 15) & ~size_t(15));
+int64_t gc_spmm_default_panel_cols(int64_t K, int64_t F) {
+  if (K <= 0 || F <= 0) return 1;
+  // Measured on a 2.4 M-node power-law graph (B200, 126 MB L2): the time falls
+  // with the panel width until a panel's rows of H take about 128 MB -- every
+  // cut costs a partial-sum row and shortens the pieces -- and rises again when
+  // the matrix is not cut by column at all.
+  const int64_t target_bytes = int64_t(128) << 20;
+  const int64_t cols = target_bytes / (F * 4);
+  int64_t p2 = 1024;
+  while (p2 * 2 <= cols && p2 < 262144) p2 *= 2;
+  return std::min<int64_t>(p2, std::max<int64_t>(K, 1));
 }
 
-int gc_spmm_plan_build(const int32_t* rowptr, int64_t M, void* plan, size_t plan_bytes, void* stream) {
-  GC_REQUIRE(rowptr && plan, "gc_spmm_plan_build: null pointer");
-  GC_REQUIRE(M >= 0 && M < INT32_MAX, "gc_spmm_plan_build: M=%lld out of int32 range", (long long)M);
-  GC_REQUIRE(gc::aligned16(plan), "gc_spmm_plan_build: plan must be 16-byte aligned");
-  if (plan_bytes < gc_spmm_plan_bytes(M)) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_plan_build: plan buffer too small");
+size_t gc_spmm_plan_workspace_bytes(int64_t M, int64_t n_pieces) {
+  if (M < 0 || n_pieces < 0) return 0;
+  return carve(nullptr, M, n_pieces).total;
+}
+
+int gc_spmm_plan_count(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
+                       int64_t* counts, void* workspace, size_t workspace_bytes, void* stream) {
+  GC_REQUIRE(M >= 0 && K >= 0 && M < INT32_MAX && K < INT32_MAX, "gc_spmm_plan_count: size out of int32 range");
+  GC_REQUIRE(panel_cols >= 1 && panel_cols < INT32_MAX, "gc_spmm_plan_count: panel_cols must be positive");
+  GC_REQUIRE(counts && workspace, "gc_spmm_plan_count: null pointer");
+  GC_REQUIRE(M == 0 || rowptr, "gc_spmm_plan_count: null rowptr");
+  if (workspace_bytes < gc_spmm_plan_workspace_bytes(M, 0))
+    return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_plan_count: workspace too small");
   cudaStream_t st = gc::as_stream(stream);
-  auto* hdr = reinterpret_cast<PlanHeader*>(plan);
-  auto* long_rows = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_long_rows_offset());
-  auto* seg_off = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_seg_off_offset(M));
-  if (M > 0) plan_collect_kernel<<<unsigned((M + 255) / 256), 256, 0, st>>>(rowptr, int(M), hdr, seg_off);
-  plan_scan_kernel<<<1, 1024, 0, st>>>(rowptr, int(M), hdr, long_rows, seg_off);
-  return gc::check_launch("gc_spmm_plan_build", M > 0 ? 2 : 1);
+  const PlanWs w = carve(workspace, M, 0);
+  if (M > 0) {
+    int rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), w, st);
+    if (rc != GC_OK) return rc;
+  }
+  plan_totals_kernel<<<1, 1, 0, st>>>(w.rows_pieces, w.rows_cut, w.rows_slots, w.piece_base, w.cut_base,
+                                      w.slot_base, int(M), counts);
+  return gc::check_launch("gc_spmm_plan_count");
 }
 
-size_t gc_spmm_scratch_bytes(int64_t nnz, int64_t F) {
-  if (nnz < 0 || F <= 0) return 0;
-  // every segment belongs to a row with more than GC_SPMM_LONG_ROW entries and
-  // ceil(d / SEGMENT) <= d / LONG_ROW for d > LONG_ROW (SEGMENT = 2 * LONG_ROW)
-  return size_t(nnz / GC_SPMM_LONG_ROW + 1) * size_t(scratch_ld(F)) * sizeof(float);
+size_t gc_spmm_plan_bytes(int64_t n_pieces, int64_t n_cut) {
+  if (n_pieces < 0 || n_cut < 0) return 0;
+  return sizeof(PlanHeader) + 3 * align16(size_t(n_pieces) * 4) + 3 * align16(size_t(n_cut) * 4);
+}
+
+int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
+                       int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  GC_REQUIRE(M >= 0 && K >= 0 && M < INT32_MAX && K < INT32_MAX, "gc_spmm_plan_build: size out of int32 range");
+  GC_REQUIRE(panel_cols >= 1 && panel_cols < INT32_MAX, "gc_spmm_plan_build: panel_cols must be positive");
+  GC_REQUIRE(n_pieces >= M && n_pieces < INT32_MAX && n_slots >= 0 && n_slots < INT32_MAX && n_cut >= 0 && n_cut <= M,
+             "gc_spmm_plan_build: counts are not those gc_spmm_plan_count reported");
+  GC_REQUIRE(plan && workspace, "gc_spmm_plan_build: null pointer");
+  GC_REQUIRE(gc::aligned16(plan), "gc_spmm_plan_build: plan must be 16-byte aligned");
+  if (plan_bytes < gc_spmm_plan_bytes(n_pieces, n_cut))
+    return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_plan_build: plan buffer too small");
+  if (workspace_bytes < gc_spmm_plan_workspace_bytes(M, n_pieces))
+    return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_plan_build: workspace too small");
+  cudaStream_t st = gc::as_stream(stream);
+  const PlanWs w = carve(workspace, M, n_pieces);
+  PlanView pv = plan_view(plan, n_pieces, n_cut);
+  plan_header_kernel<<<1, 1, 0, st>>>(pv.hdr, int(M), int(n_pieces), int(n_slots), int(n_cut), int(panel_cols));
+  int rc = gc::check_launch("spmm plan: header");
+  if (rc != GC_OK || M == 0) return rc;
+  if ((rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), w, st)) != GC_OK) return rc;
+  const unsigned gm = unsigned((M + 255) / 256), gp = unsigned((n_pieces + 255) / 256);
+  plan_emit_kernel<<<gm, 256, 0, st>>>(rowptr, col, int(M), int(K), int(panel_cols), w.rows_cut, w.piece_base,
+                                       w.cut_base, w.slot_base, w.rows_pieces, w.keys, w.ids, w.u_start, w.u_len,
+                                       w.u_target, pv.cut_row, pv.cut_slot0, pv.cut_nslots);
+  if ((rc = gc::check_launch("spmm plan: emit")) != GC_OK) return rc;
+  cub::DoubleBuffer<uint64_t> dk(w.keys, w.keys_alt);
+  cub::DoubleBuffer<int32_t> dv(w.ids, w.ids_alt);
+  const int n_panels = int((K + panel_cols - 1) / panel_cols);
+  int phase_bits = 1;
+  while ((1 << phase_bits) <= n_panels) ++phase_bits;
+  size_t need = 0;
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, need, dk, dv, int(n_pieces), 0, 32 + phase_bits, st);
+  if (e == cudaSuccess && need > w.cub_bytes)
+    return gc::fail(GC_ERR_WORKSPACE, "spmm plan: sort needs %zu bytes of temporary storage, have %zu", need,
+                    w.cub_bytes);
+  size_t b = w.cub_bytes;
+  if (e == cudaSuccess) e = cub::DeviceRadixSort::SortPairs(w.cub, b, dk, dv, int(n_pieces), 0, 32 + phase_bits, st);
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "spmm plan: sort: %s", cudaGetErrorString(e));
+  gc::count_launches(4);
+  plan_gather_kernel<<<gp, 256, 0, st>>>(dv.Current(), int(n_pieces), w.u_start, w.u_len, w.u_target, pv.start,
+                                         pv.len, pv.target);
+  return gc::check_launch("spmm plan: gather");
+}
+
+size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F) {
+  if (n_slots < 0 || F <= 0) return 0;
+  return std::max<size_t>(size_t(n_slots) * size_t(scratch_ld(F)) * sizeof(float), 256);
 }
 
 int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
                     const float* H, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
-                    float* mask, const void* plan, void* scratch, size_t scratch_bytes, void* stream) {
+                    float* mask, const void* plan, int64_t n_pieces, int64_t n_cut, void* scratch,
+                    size_t scratch_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && F >= 0, "gc_spmm_csr_f32: negative size");
   GC_REQUIRE(M < INT32_MAX && K < INT32_MAX && F < INT32_MAX, "gc_spmm_csr_f32: size out of int32 range");
+  GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_ACCUMULATE)) == 0, "gc_spmm_csr_f32: unknown epilogue bits");
   if (M == 0 || F == 0) return GC_OK;
   GC_REQUIRE(rowptr && Y, "gc_spmm_csr_f32: null rowptr/Y");
   GC_REQUIRE(ldY >= F && (K == 0 || ldH >= F), "gc_spmm_csr_f32: leading dimension smaller than F");
   GC_REQUIRE(K == 0 || H, "gc_spmm_csr_f32: null H");
-  GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_ACCUMULATE)) == 0, "gc_spmm_csr_f32: unknown epilogue bits");
   cudaStream_t st = gc::as_stream(stream);
   Epilogue ep{bias, mask, (epilogue & GC_EPI_RELU) ? 1 : 0, (epilogue & GC_EPI_ACCUMULATE) ? 1 : 0};
 
   const bool vec4 = (F % 4 == 0) && (ldH % 4 == 0) && (ldY % 4 == 0) && gc::aligned16(H) && gc::aligned16(Y) &&
                     (!bias || gc::aligned16(bias)) && (!mask || gc::aligned16(mask));
-  const int skip_long = plan ? 1 : 0;
-  if (plan) {
+  const bool planned = plan != nullptr;
+  const int32_t *ps = nullptr, *pl = nullptr, *pt = nullptr;
+  PlanView pv{};
+  int np = int(M), cap = 0;
+  const int64_t ldS = scratch_ld(F);
+  if (planned) {
     GC_REQUIRE(gc::aligned16(plan), "gc_spmm_csr_f32: plan must be 16-byte aligned");
-    if (!scratch) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: plan given but scratch is null");
-    GC_REQUIRE(gc::aligned16(scratch), "gc_spmm_csr_f32: scratch must be 16-byte aligned");
+    GC_REQUIRE(n_pieces >= M && n_pieces < INT32_MAX && n_cut >= 0 && n_cut <= M,
+               "gc_spmm_csr_f32: n_pieces / n_cut do not describe a plan of this matrix");
+    pv = plan_view(const_cast<void*>(plan), n_pieces, n_cut);
+    ps = pv.start;
+    pl = pv.len;
+    pt = pv.target;
+    np = int(n_pieces);
+    if (n_cut > 0) {
+      if (!scratch) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: the plan cuts rows but scratch is null");
+      GC_REQUIRE(gc::aligned16(scratch), "gc_spmm_csr_f32: scratch must be 16-byte aligned");
+      const size_t rows = scratch_bytes / (size_t(ldS) * sizeof(float));
+      cap = rows > size_t(INT32_MAX) ? INT32_MAX : int(rows);
+      if (cap < 1) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: scratch too small");
+    }
   }
+  float* sc = static_cast<float*>(scratch);
   if (vec4)
-    dispatch_rows<4>(rowptr, col, val, int(M), int(F), H, ldH, Y, ldY, ep, skip_long, st);
+    dispatch_vec4(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ep, st);
   else
-    dispatch_rows<1>(rowptr, col, val, int(M), int(F), H, ldH, Y, ldY, ep, skip_long, st);
-  int rc = gc::check_launch("gc_spmm_csr_f32 (rows)");
+    dispatch_scalar(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ep, st);
+  int rc = gc::check_launch("gc_spmm_csr_f32 (pieces)");
   if (rc != GC_OK) return rc;
-
-  if (plan) {
-    const auto* hdr = reinterpret_cast<const PlanHeader*>(plan);
-    const auto* long_rows = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_long_rows_offset());
-    const auto* seg_off = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_seg_off_offset(M));
-    const int64_t ldS = scratch_ld(F);
-    // The segment count lives on the device; the scratch must hold the bound
-    // gc_spmm_scratch_bytes() gives for this structure's nnz, which the caller
-    // knows.  A scratch smaller than one segment row is certainly wrong.
-    if (scratch_bytes < size_t(ldS) * sizeof(float))
-      return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: scratch too small");
-    float* sc = static_cast<float*>(scratch);
-    const size_t cap_rows = scratch_bytes / (size_t(ldS) * sizeof(float));
-    const int cap = cap_rows > size_t(INT32_MAX) ? INT32_MAX : int(cap_rows);
-    if (vec4)
-      dispatch_segments<4>(rowptr, col, val, int(F), H, ldH, hdr, long_rows, seg_off, sc, ldS, cap, st);
-    else
-      dispatch_segments<1>(rowptr, col, val, int(F), H, ldH, hdr, long_rows, seg_off, sc, ldS, cap, st);
-    rc = gc::check_launch("gc_spmm_csr_f32 (segments)");
-    if (rc != GC_OK) return rc;
-    spmm_finalize_kernel<<<gc::kNumSMs * 2, 256, 0, st>>>(int(F), hdr, long_rows, seg_off, sc, ldS, Y, ldY, ep);
+  if (planned && n_cut > 0) {
+    const unsigned g = unsigned(std::min<int64_t>((n_cut + 7) / 8, gc::kNumSMs * 8));
+    spmm_finalize_kernel<<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
+                                            cap, Y, ldY, ep);
     rc = gc::check_launch("gc_spmm_csr_f32 (finalize)");
   }
   return rc;
@@ -523,26 +667,27 @@ int static_scratch_for_current_device(float** out) {
 }  // namespace
 
 int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K,
-                            int64_t F, int64_t nnz, const float* H, int64_t ldH, const float* bias, int epilogue,
-                            float* Y, int64_t ldY, float* mask, const void* plan, void* stream) {
-  GC_REQUIRE(nnz >= 0, "gc_spmm_csr_f32_noalloc: negative nnz");
-  if (!plan)  // no long-row segments, hence no scratch at all
-    return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, nullptr, nullptr, 0,
-                           stream);
-  const size_t need = gc_spmm_scratch_bytes(nnz, F);
+                            int64_t F, const float* H, int64_t ldH, const float* bias, int epilogue, float* Y,
+                            int64_t ldY, float* mask, const void* plan, int64_t n_pieces, int64_t n_slots,
+                            int64_t n_cut, void* stream) {
+  GC_REQUIRE(n_slots >= 0, "gc_spmm_csr_f32_noalloc: negative n_slots");
+  if (!plan || n_cut == 0)  // no cut rows, hence no scratch at all
+    return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, n_pieces, n_cut,
+                           nullptr, 0, stream);
+  const size_t need = gc_spmm_scratch_bytes(n_slots, F);
   if (need > size_t(GC_SPMM_STATIC_SCRATCH_BYTES))
     return gc::fail(GC_ERR_WORKSPACE,
-                    "gc_spmm_csr_f32_noalloc: nnz=%lld, F=%lld needs up to %zu bytes of scratch, the built-in "
-                    "buffer holds %zu; use gc_spmm_csr_f32 with caller-provided scratch",
-                    (long long)nnz, (long long)F, need, size_t(GC_SPMM_STATIC_SCRATCH_BYTES));
+                    "gc_spmm_csr_f32_noalloc: %lld partial-sum rows of F=%lld need %zu bytes of scratch, the "
+                    "built-in buffer holds %zu; use gc_spmm_csr_f32 with caller-provided scratch",
+                    (long long)n_slots, (long long)F, need, size_t(GC_SPMM_STATIC_SCRATCH_BYTES));
   float* scratch = nullptr;
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc != GC_OK) return rc;
   // Every partial-sum row the finalize pass reads is fully written by the
-  // segment pass of the same call, so stale contents of the shared buffer are
+  // piece pass of the same call, so stale contents of the shared buffer are
   // never observed and nothing has to be cleared.
-  return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, scratch,
-                         size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
+  return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, n_pieces, n_cut,
+                         scratch, size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

@@ -51,21 +51,39 @@ const char* gc_status_string(int status);
  * adjacency) as used by gcn_conv_forward / gcn_conv_backward
  * (src/graphcuda/cuda/gcn.cu:12,40,49).
  *
- * A "plan" is derived once per CSR structure: the list of long rows (more
- * than GC_SPMM_LONG_ROW non-zeros) and their split into fixed-size segments,
- * so that heavy-tailed degree distributions do not serialise on one warp.
- * The plan lives in caller memory of gc_spmm_plan_bytes(M) bytes and only
- * depends on rowptr.
+ * A "plan" is derived once per CSR structure (and column-panel width).  It
+ * lists the matrix as pieces -- contiguous runs of non-zeros of one row --
+ * in the order they are processed:
+ *   - rows with more than GC_SPMM_PANEL_MIN_ROW non-zeros are cut at column
+ *     panel boundaries (panel_cols columns per panel) and the pieces are
+ *     processed panel by panel, so the gathers of a phase hit one slab of H
+ *     that stays in the L2;
+ *   - pieces longer than GC_SPMM_SEGMENT are cut further, so heavy rows are
+ *     spread over many warps;
+ *   - within a phase pieces are ordered by decreasing length.
+ * Pieces of cut rows write partial sums ("slots") to scratch; a second pass
+ * adds them in a fixed order.  Building is two calls because the sizes depend
+ * on the data: gc_spmm_plan_count -> read the three counts -> allocate ->
+ * gc_spmm_plan_build.
  */
-#define GC_SPMM_LONG_ROW 1024 /* rows with more non-zeros than this take the segmented path */
-#define GC_SPMM_SEGMENT 2048  /* non-zeros per segment of a long row */
+#define GC_SPMM_PANEL_MIN_ROW 128 /* rows with more non-zeros than this are cut at panel boundaries */
+#define GC_SPMM_SEGMENT 2048      /* longest piece, in non-zeros */
 
-size_t gc_spmm_plan_bytes(int64_t M);
-/* Builds the plan on `stream`.  plan must be 16-byte aligned device memory. */
-int gc_spmm_plan_build(const int32_t* rowptr, int64_t M, void* plan, size_t plan_bytes, void* stream);
-/* Upper bound of the scratch gc_spmm_csr_f32 needs for a structure with nnz
- * non-zeros and F feature columns (partial sums of long-row segments). */
-size_t gc_spmm_scratch_bytes(int64_t nnz, int64_t F);
+/* Default panel width (columns): a power of two for which panel_cols rows of H
+ * (F fp32 each) take about 128 MB, at most 262144 and at most K. */
+int64_t gc_spmm_default_panel_cols(int64_t K, int64_t F);
+/* Scratch for plan construction; pass n_pieces = 0 for gc_spmm_plan_count. */
+size_t gc_spmm_plan_workspace_bytes(int64_t M, int64_t n_pieces);
+/* counts (device, int64[3]) <- {n_pieces, n_slots, n_cut}. */
+int gc_spmm_plan_count(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
+                       int64_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+size_t gc_spmm_plan_bytes(int64_t n_pieces, int64_t n_cut);
+/* plan: 16-byte aligned device memory of gc_spmm_plan_bytes(n_pieces, n_cut). */
+int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
+                       int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
+                       void* workspace, size_t workspace_bytes, void* stream);
+/* Scratch gc_spmm_csr_f32 needs with a plan of n_slots slots and F feature columns. */
+size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F);
 
 #define GC_EPI_RELU 1        /* out = max(out, 0) computed as out * (out > 0), reference gcn.cu:19-20 */
 #define GC_EPI_ACCUMULATE 2  /* out += result instead of out = result (bias/relu applied after the add) */
@@ -73,8 +91,9 @@ size_t gc_spmm_scratch_bytes(int64_t nnz, int64_t F);
 /*
  * Y[M,F] = A_csr[M,K] * H[K,F] (+ bias[F]) (ReLU).  mask, when non-null,
  * receives (pre-activation > 0) as 0.0f/1.0f with leading dimension ldY
- * (the fp32 mask of reference gcn.cu:19).  plan may be null: then every row
- * takes the row-per-warp path.  scratch may be null only when plan is null.
+ * (the fp32 mask of reference gcn.cu:19).  plan may be null: then every row is
+ * one piece in natural order (n_pieces, n_cut ignored, no scratch needed).
+ * With a plan, n_pieces and n_cut are the counts it was built with.
  * No atomics: results are deterministic run to run.
  */
 int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
@@ -82,7 +101,8 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
                     const float* H, int64_t ldH,
                     const float* bias, int epilogue,
                     float* Y, int64_t ldY, float* mask,
-                    const void* plan, void* scratch, size_t scratch_bytes,
+                    const void* plan, int64_t n_pieces, int64_t n_cut,
+                    void* scratch, size_t scratch_bytes,
                     void* stream);
 
 /*
@@ -92,13 +112,13 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
  * every call, spmm_cusparse.cu:100-103).  Some hosts of this library cannot
  * call cudaMalloc at the point where they need the product: a real-time or
  * serving loop with a frozen memory budget, a plugin whose host application
- * owns all device memory and hands out only the input and output buffers.  For them the long-row scratch lives in a
- * fixed buffer inside the library image: GC_SPMM_STATIC_SCRATCH_BYTES bytes of
- * device memory on every GPU that loads the library, held until the process
- * exits.  The caller still passes the CSR arrays, H, Y (and the plan, which it
- * built once into memory it owns).
+ * owns all device memory and hands out only the input and output buffers.
+ * For them the partial-sum scratch lives in a fixed buffer inside the library
+ * image: GC_SPMM_STATIC_SCRATCH_BYTES bytes of device memory on every GPU that
+ * loads the library, held until the process exits.  The caller still passes
+ * the CSR arrays, H, Y (and the plan, which it built once into memory it owns).
  *
- *  - Limit: gc_spmm_scratch_bytes(nnz, F) must not exceed
+ *  - Limit: gc_spmm_scratch_bytes(n_slots, F) must not exceed
  *    GC_SPMM_STATIC_SCRATCH_BYTES; larger problems are refused with
  *    GC_ERR_WORKSPACE and a message, never truncated.
  *  - The first call on a device looks up the buffer's device address
@@ -113,11 +133,12 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
  */
 #define GC_SPMM_STATIC_SCRATCH_BYTES (8u << 20)
 int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val,
-                            int64_t M, int64_t K, int64_t F, int64_t nnz,
+                            int64_t M, int64_t K, int64_t F,
                             const float* H, int64_t ldH,
                             const float* bias, int epilogue,
                             float* Y, int64_t ldY, float* mask,
-                            const void* plan, void* stream);
+                            const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                            void* stream);
 
 /* ---- dense GEMM --------------------------------------------------------- */
 

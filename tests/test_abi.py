@@ -56,19 +56,26 @@ def test_argument_validation_without_gpu():
     # leading dimension too small
     assert L.gc_gemm_f32(0, 0, 8, 8, 8, 16, 4, 16, 8, 16, 8, None, 0, None, 0, None, 0, None) == -1
     # unknown epilogue bit
-    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, None, 0, None) == -1
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, 0, 0, None, 0, None) == -1
     # empty problems succeed without launching anything
     assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, 0, None, 0, None) == 0
-    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, None) == 0
+    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, 0, 0, None, 0, None) == 0
     with pytest.raises(RuntimeError):
         _lib.check(-1, "probe")
 
 
 def test_plan_and_workspace_sizes():
     L = _lib.lib()
-    assert L.gc_spmm_plan_bytes(0) >= 16
-    assert L.gc_spmm_plan_bytes(1000) >= 16 + 4 * 1000 + 4 * 1001
-    assert L.gc_spmm_scratch_bytes(10_000_000, 256) >= (10_000_000 // 1024) * 256 * 4
+    assert L.gc_spmm_plan_bytes(0, 0) >= 32
+    assert L.gc_spmm_plan_bytes(1000, 10) >= 32 + 3 * 4 * 1000 + 3 * 4 * 10
+    assert L.gc_spmm_plan_workspace_bytes(1000, 0) >= 6 * 4 * 1000
+    assert L.gc_spmm_plan_workspace_bytes(1000, 5000) >= 6 * 4 * 1000 + 36 * 5000
+    assert L.gc_spmm_scratch_bytes(10_000, 256) == 10_000 * 256 * 4
+    assert L.gc_spmm_scratch_bytes(10, 47) == 10 * 48 * 4  # rows padded to 16 bytes
+    # panel width: a power of two whose rows of H take about 128 MiB, at most 262144 and never more than K
+    assert L.gc_spmm_default_panel_cols(2_449_029, 256) == 131072
+    assert L.gc_spmm_default_panel_cols(2_449_029, 48) == 262144
+    assert L.gc_spmm_default_panel_cols(2708, 16) == 2708
     assert L.gc_gemm_workspace_bytes(0, 0, 4096, 256, 256, _lib.PREC_TF32X3) >= 256 + 2 * 256 * 256 * 4
 
 

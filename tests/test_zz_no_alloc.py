@@ -18,13 +18,15 @@ from tests.helpers import random_csr, to_gpu_csr
 pytestmark = pytest.mark.gpu
 
 
-def _call_noalloc(L, adj, H, Y, bias=None, epilogue=0, nnz=None):
+def _call_noalloc(L, adj, H, Y, bias=None, epilogue=0, n_slots=None):
     M, K = adj.shape
     F = H.size(1)
+    plan = adj.plan_for(F)
     return L.gc_spmm_csr_f32_noalloc(
-        adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), M, K, F, adj.nnz if nnz is None else nnz,
+        adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), M, K, F,
         H.data_ptr(), F, bias.data_ptr() if bias is not None else None, epilogue, Y.data_ptr(), F, None,
-        adj.plan.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        plan.buf.data_ptr(), plan.n_pieces, plan.n_slots if n_slots is None else n_slots, plan.n_cut,
+        torch.cuda.current_stream().cuda_stream)
 
 
 def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(cuda):
@@ -33,7 +35,7 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(cuda):
     # long rows of several segments so the scratch is really used
     A = random_csr(6000, 9000, 6.0, seed=31, long_rows=((5, 1500), (77, 5000), (5999, 8000)))
     adj = to_gpu_csr(A, cuda)
-    assert adj.plan_counts()[1] >= 1 + 3 + 4
+    assert adj.plan_counts(64)[1] >= 3 + 4  # partial-sum slots of the two rows above 2048 non-zeros
     g = torch.Generator().manual_seed(3)
     for F, relu in ((64, False), (256, True)):
         H1 = torch.randn(9000, F, generator=g).to(cuda)
@@ -54,12 +56,12 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(cuda):
 def test_noalloc_refuses_what_does_not_fit(cuda):
     from graphcuda_b200 import _lib
     L = _lib.lib()
-    A = random_csr(500, 500, 4.0, seed=1, long_rows=((1, 480),))
-    adj = to_gpu_csr(A, cuda)
-    H = torch.randn(500, 32, device=cuda)
     Y = torch.empty(500, 32, device=cuda)
-    # pretend the structure holds far more non-zeros than the built-in scratch can serve
-    too_many = (_lib.SPMM_STATIC_SCRATCH_BYTES // (32 * 4) + 8) * 1024
-    st = _call_noalloc(L, adj, H, Y, nnz=too_many)
+    A = random_csr(500, 5000, 4.0, seed=1, long_rows=((1, 4500),))
+    adj = to_gpu_csr(A, cuda)
+    H = torch.randn(5000, 32, device=cuda)
+    # claim more partial-sum rows than the built-in scratch can hold
+    too_many = _lib.SPMM_STATIC_SCRATCH_BYTES // (32 * 4) + 8
+    st = _call_noalloc(L, adj, H, Y, n_slots=too_many)
     assert st == -4 and b"built-in" in L.gc_last_error()
     assert L.gc_spmm_scratch_bytes(too_many, 32) > _lib.SPMM_STATIC_SCRATCH_BYTES
