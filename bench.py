@@ -401,7 +401,7 @@ def run_ours(args):
     peak, peak_src = measured_peaks()
     achieved = sp_bytes / (sp_ms * 1e-3) / 1e9 if sp_ms > 0 else 0.0
     roofline = {
-        "kernel": "spmm_rows_kernel (+ long-row segment and finalize kernels)",
+        "kernel": "spmm_pieces_kernel (+ spmm_finalize_kernel)",
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
         "peak_source": peak_src,
         "bytes": "compulsory: 4(M+1) + 8 nnz + 4 K F + 4 M F per launch",

@@ -125,8 +125,11 @@ class CSRAdjacency:
             epi |= EPI_ACCUMULATE
         if out is None:
             out = torch.empty((M, F), dtype=torch.float32, device=dev)
-        _require(tuple(out.shape) == (M, F) and out.dtype == torch.float32 and out.is_contiguous(),
-                 "out has the wrong shape, dtype or layout")
+        # `out` may be a column slice of a wider row-major matrix (unit column stride)
+        _require(tuple(out.shape) == (M, F) and out.dtype == torch.float32 and out.stride(1) == 1
+                 and (M <= 1 or out.stride(0) >= F), "out has the wrong shape, dtype or layout")
+        ldy = out.stride(0) if M > 1 else max(F, 1)
+        _require(not want_mask or ldy == F, "a mask needs a contiguous output")
         mask = torch.empty((M, F), dtype=torch.float32, device=dev) if want_mask else None
         if bias is not None:
             _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == F, "bias must be float32 [F]")
@@ -142,7 +145,7 @@ class CSRAdjacency:
             ldh = H.stride(0) if H.size(0) > 1 else max(F, 1)
             st = L.gc_spmm_csr_f32(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
                                    H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None, epi,
-                                   out.data_ptr(), F, mask.data_ptr() if mask is not None else None,
+                                   out.data_ptr(), ldy, mask.data_ptr() if mask is not None else None,
                                    plan.buf.data_ptr() if plan is not None else None,
                                    plan.n_pieces if plan is not None else 0, plan.n_cut if plan is not None else 0,
                                    scratch.data_ptr() if scratch is not None else None,

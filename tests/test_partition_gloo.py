@@ -29,6 +29,9 @@ class TorchCPUBackend:
             y = y + bias
         if relu:
             y = y * (y > 0)
+        if accumulate_into is not None:  # in place, like the CUDA kernel
+            accumulate_into.copy_(y)
+            return accumulate_into
         return y
 
     def gemm(self, A, B, *, bias=None, relu=False, precision=None):

@@ -60,7 +60,7 @@ def _worker(rank, world, port, n, dims, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n,dims", [(5000, [24, 32, 32, 7]), (3001, [40, 16, 5])])
+@pytest.mark.parametrize("n,dims", [(5000, [24, 32, 32, 7]), (3001, [40, 16, 5]), (4000, [24, 128, 256, 7])])
 def test_two_gpu_partition_matches_oracle(n, dims):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
