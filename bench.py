@@ -410,14 +410,12 @@ def run_ours(args):
         "per_feature_width": {str(F): {"ms": d[0] / d[2], "gbs": d[1] / (d[0] * 1e-3) / 1e9, "launches": d[2]}
                               for F, d in sorted(per_f.items())},
         "share_of_step": sp_ms / args.steps / ms_step if ms_step > 0 else None,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of the F = 256 launch (pieces + finalize kernels), captured
+        # with ncu on the half-size graph and scaled by the non-zeros (profiles/spmm_pieces_kernel_rmat_products.md);
+        # the compulsory bytes of that launch are 6.04e9
+        "traffic": 21.8e9 if (args.shrink == 1 and world == 1) else None,
+        "traffic_note": "bytes per F=256 launch at full size on 1 GPU; compulsory 6.04e9",
     }
-    prof = os.path.join(ROOT, "profiles", "spmm_traffic.json")
-    if os.path.exists(prof):
-        try:
-            roofline["traffic"] = json.load(open(prof))
-        except Exception:
-            pass
 
     line = {
         "metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
