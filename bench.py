@@ -313,12 +313,11 @@ def run_ours(args):
 
     def step(Xd, yd, Xg):
         opt.zero_grad(set_to_none=True)
+        # log_softmax + NLL over all nodes, fused (mean over the n nodes of the whole graph)
         if world == 1:
-            out = model(Xd, adj)
-            loss = torch.nn.functional.nll_loss(out, yd)
+            loss = gc.log_softmax_nll_loss(model(Xd, adj, log_softmax=False), yd, scale=1.0 / n)
         else:
-            out = model(Xd, part, X_gathered=Xg)
-            loss = torch.nn.functional.nll_loss(out, yd, reduction="sum") / n
+            loss = gc.log_softmax_nll_loss(model(Xd, part, X_gathered=Xg, log_softmax=False), yd, scale=1.0 / n)
         loss.backward()
         opt.step()
         return loss

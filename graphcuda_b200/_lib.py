@@ -44,6 +44,11 @@ SIGNATURES = {
     "gc_relu_backward_f32": (_int, [_f32p, _i64, _f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
     "gc_mask_mul_f32": (_int, [_f32p, _i64, _f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
     "gc_transpose_f32": (_int, [_f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
+    "gc_nll_workspace_bytes": (_size, [_i64]),
+    "gc_logsoftmax_nll_forward_f32": (_int, [_f32p, _i64, _i64p, _void, _i64, _i64, C.c_float, _f32p, _void, _size,
+                                             _void]),
+    "gc_logsoftmax_nll_backward_f32": (_int, [_f32p, _i64, _i64p, _void, _i64, _i64, C.c_float, _f32p, _f32p, _i64,
+                                              _void, _void]),
     "gc_coo_rows_to_rowptr": (_int, [_i64p, _i64, _i64, _i32p, _void]),
     "gc_narrow_i64_i32": (_int, [_i64p, _i32p, _i64, _void]),
     "gc_gcn_norm_f32": (_int, [_i64p, _i64p, _i64, _i64, _f32p, _f32p, _void]),

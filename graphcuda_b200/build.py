@@ -31,6 +31,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "elementwise.cu",
     "graph_build.cu",
+    "loss.cu",
 ]
 
 NVCC_FLAGS = [

@@ -17,7 +17,9 @@ class GCN(torch.nn.Module):
             [GCNConv(dims[i], dims[i + 1], apply_relu=(i < len(dims) - 2), precision=precision)
              for i in range(len(dims) - 1)])
 
-    def forward(self, x, adj):
+    def forward(self, x, adj, log_softmax: bool = True):
+        """log_softmax=False returns the last layer's raw output, for
+        losses.log_softmax_nll_loss which fuses the normalisation with the loss."""
         for conv in self.convs:
             x = conv(x, adj)
-        return torch.log_softmax(x, dim=1)
+        return torch.log_softmax(x, dim=1) if log_softmax else x

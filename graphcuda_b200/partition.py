@@ -255,10 +255,10 @@ class DistGCN(torch.nn.Module):
             w.uniform_(-s, s)  # same initialiser as src/graphcuda/python/gcn.py:43-45
             self.weights.append(torch.nn.Parameter(w))
 
-    def forward(self, X_local, graph: PartitionedGraph, X_gathered=None):
+    def forward(self, X_local, graph: PartitionedGraph, X_gathered=None, log_softmax: bool = True):
         h = X_local
         last = len(self.weights) - 1
         for i, W in enumerate(self.weights):
             h = DistGCNConvFunction.apply(h, graph, W, i < last, None, self.precision,
                                           X_gathered if i == 0 else None)
-        return torch.log_softmax(h, dim=1)
+        return torch.log_softmax(h, dim=1) if log_softmax else h

@@ -190,6 +190,26 @@ int gc_mask_mul_f32(const float* dY, int64_t lddy, const float* mask, int64_t ld
 int gc_transpose_f32(const float* in, int64_t ldin, float* out, int64_t ldout,
                      int64_t M, int64_t N, void* stream);
 
+/* ---- classification tail (reference tests/gcn/graphcuda_impl.py:24,55) ---- */
+
+/*
+ * loss = scale * sum over rows r with row_mask[r] != 0 (all rows when row_mask
+ * is null) of -log_softmax(Z[r, :])[labels[r]]: torch.log_softmax followed by
+ * F.nll_loss on the masked rows as the reference's script computes them
+ * (scale = 1 / number of selected rows gives reduction='mean').  The
+ * workspace (gc_nll_workspace_bytes(M)) keeps the per-row logsumexp for the
+ * backward call.  loss: one device float.
+ */
+size_t gc_nll_workspace_bytes(int64_t M);
+int gc_logsoftmax_nll_forward_f32(const float* Z, int64_t ldz, const int64_t* labels, const uint8_t* row_mask,
+                                  int64_t M, int64_t C, float scale, float* loss,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+/* dZ = grad_loss * scale * (softmax(Z) - onehot(labels)) on selected rows, 0
+ * elsewhere; grad_loss is one device float (null: 1). */
+int gc_logsoftmax_nll_backward_f32(const float* Z, int64_t ldz, const int64_t* labels, const uint8_t* row_mask,
+                                   int64_t M, int64_t C, float scale, const float* grad_loss,
+                                   float* dZ, int64_t lddz, const void* workspace, void* stream);
+
 /* ---- adjacency construction (reference tests/gcn/graphcuda_impl.py:27-38) - */
 
 /*
