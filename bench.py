@@ -477,11 +477,17 @@ def aux_measurements(dev, args):
 
     def cora_step():
         opt.zero_grad(set_to_none=True)
-        loss = torch.nn.functional.nll_loss(model(X, adj)[train], y[train])
+        loss = gc.log_softmax_nll_loss(model(X, adj, log_softmax=False), y, train, scale=1.0 / 140)
         loss.backward()
         opt.step()
 
     out["cora_like_2layer_train_epoch_ms"] = _time_ms(cora_step, warm=5, iters=20)
+    # the same step recorded once as a CUDA graph and replayed (launch-bound workload)
+    torch.manual_seed(0)
+    model_g = GCN([c["features"], c["hidden"], c["classes"]]).to(dev)
+    opt_g = torch.optim.Adam(model_g.parameters(), lr=0.01, capturable=True)
+    graphed = gc.GraphedTrainStep(model_g, adj, X, y, opt_g, row_mask=train)
+    out["cora_like_2layer_train_epoch_ms_cuda_graph"] = _time_ms(graphed.step, warm=5, iters=50)
 
     # arxiv-shaped CSR aggregation, F = 128 / 256 (fused bias + ReLU)
     c = synth.CONFIGS["rmat_arxiv"]

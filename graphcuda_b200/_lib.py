@@ -27,9 +27,10 @@ SIGNATURES = {
     "gc_status_string": (C.c_char_p, [_int]),
     "gc_spmm_default_panel_cols": (_i64, [_i64, _i64]),
     "gc_spmm_plan_workspace_bytes": (_size, [_i64, _i64]),
-    "gc_spmm_plan_count": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64p, _void, _size, _void]),
+    "gc_spmm_default_segment": (_i64, [_i64]),
+    "gc_spmm_plan_count": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64, _i64p, _void, _size, _void]),
     "gc_spmm_plan_bytes": (_size, [_i64, _i64]),
-    "gc_spmm_plan_build": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64, _i64, _i64, _void, _size, _void, _size,
+    "gc_spmm_plan_build": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _void, _size, _void, _size,
                                   _void]),
     "gc_spmm_scratch_bytes": (_size, [_i64, _i64]),
     "gc_spmm_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p, _i64,

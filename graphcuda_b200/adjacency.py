@@ -48,6 +48,7 @@ class CSRAdjacency:
         self.device = rowptr.device
         self._symmetric = symmetric
         self.use_plan = bool(build_plan)
+        self.segment = None  # longest piece in non-zeros; None: gc_spmm_default_segment(nnz)
         self._plans = {}  # panel_cols -> SpmmPlan
 
     def plan_for(self, F: int, panel_cols: Optional[int] = None):
@@ -60,13 +61,14 @@ class CSRAdjacency:
         hit = self._plans.get(panel_cols)
         if hit is not None:
             return hit
+        seg = int(L.gc_spmm_default_segment(self.nnz)) if self.segment is None else int(self.segment)
         dev = self.device
         with torch.cuda.device(dev):
             s = _stream(dev)
             counts = torch.zeros(3, dtype=torch.int64, device=dev)
             wsb = L.gc_spmm_plan_workspace_bytes(M, 0)
             ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
-            _lib.check(L.gc_spmm_plan_count(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols,
+            _lib.check(L.gc_spmm_plan_count(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols, seg,
                                             counts.data_ptr(), ws.data_ptr(), wsb, s), "gc_spmm_plan_count")
             n_pieces, n_slots, n_cut = (int(x) for x in counts.tolist())  # the one host read of plan building
             del ws
@@ -74,7 +76,7 @@ class CSRAdjacency:
             plan = torch.empty(pbytes, dtype=torch.uint8, device=dev)
             wsb = L.gc_spmm_plan_workspace_bytes(M, n_pieces)
             ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
-            _lib.check(L.gc_spmm_plan_build(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols,
+            _lib.check(L.gc_spmm_plan_build(self.rowptr.data_ptr(), self.col.data_ptr(), M, K, panel_cols, seg,
                                             n_pieces, n_slots, n_cut, plan.data_ptr(), pbytes, ws.data_ptr(), wsb,
                                             s), "gc_spmm_plan_build")
             torch.cuda.current_stream(dev).synchronize()  # ws is released below

@@ -124,8 +124,9 @@ int simt_splits(int64_t M, int64_t N, int64_t K) {
   const bool narrow = N <= 32;
   const int64_t bm = narrow ? 128 : 64, bn = narrow ? 32 : 64;
   const int64_t tiles = ceil_div(M, bm) * ceil_div(N, bn);
-  if (tiles >= kNumSMs || K < 4096) return 1;
-  int64_t splits = std::min<int64_t>(ceil_div(2 * kNumSMs, tiles), ceil_div(K, 1024));
+  // few output tiles (narrow products of the small graphs, weight gradients): spread K over the SMs
+  if (tiles >= kNumSMs || K < 256) return 1;
+  int64_t splits = std::min<int64_t>(ceil_div(2 * kNumSMs, tiles), ceil_div(K, 64));
   return int(std::max<int64_t>(1, std::min<int64_t>(splits, 512)));
 }
 

@@ -34,7 +34,11 @@
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;      // fp32 per 128-byte swizzle row
+// K extent of a stage: 32 fp32 (128-byte rows, 128-byte swizzle) or, where
+// that leaves only two stages of shared memory, 16 fp32 (64-byte rows,
+// 64-byte swizzle) for twice as many stages in flight.
+template <int BN, int PASSES>
+constexpr int block_k() { return (PASSES == 3 && BN == 256) ? 16 : 32; }
 constexpr int UMMA_K = 8;   // K of one kind::tf32 instruction
 constexpr int kThreads = 384;
 constexpr uint32_t kWaitLimit = 1u << 24;
@@ -141,8 +145,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= uint64_t(layout_type) << 61;
   return d;
 }
+// K-major tiles with 16 fp32 per row use the 64-byte swizzle (layout type 4):
+// 8-row groups are 512 bytes apart.
+template <int BK>
 __device__ __forceinline__ uint64_t smem_desc_operand(uint32_t saddr, bool mn_major, uint32_t mn_chunk) {
-  return mn_major ? smem_desc(saddr, mn_chunk, 512u, 1u) : smem_desc(saddr, 0u, 1024u, 2u);
+  if (mn_major) return smem_desc(saddr, mn_chunk, 512u, 1u);
+  return BK == 32 ? smem_desc(saddr, 0u, 1024u, 2u) : smem_desc(saddr, 0u, 512u, 4u);
 }
 
 // Instruction descriptor for kind::tf32 with fp32 accumulation.
@@ -170,6 +178,7 @@ struct TcParams {
 
 template <int BN, int PASSES>
 struct Cfg {
+  static constexpr int BK = block_k<BN, PASSES>();
   static constexpr int kABytes = BM * BK * 4;
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kABytes + kBBytes);
@@ -190,6 +199,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                  const __grid_constant__ CUtensorMap mapBlo, TcParams p) {
   using C_ = Cfg<BN, PASSES>;
   constexpr int S = C_::kStages;
+  constexpr int BK = C_::BK;
   constexpr bool kConvB = CONV_B && PASSES == 3;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -313,10 +323,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           if (!mbar_wait(bar_full(s), ph, abort_p)) { ok = false; break; }
           if (PASSES == 3 && !mbar_wait(bar_conv(s), ph, abort_p)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = smem_desc_operand(sA(s), A_MN, kMnLbo);
-          const uint64_t db = smem_desc_operand(sB(s), B_MN, kMnLbo);
-          const uint64_t dal = smem_desc_operand(sAlo(s), A_MN, kMnLbo);
-          const uint64_t dbl = smem_desc_operand(sBlo(s), B_MN, kMnLbo);
+          const uint64_t da = smem_desc_operand<BK>(sA(s), A_MN, kMnLbo);
+          const uint64_t db = smem_desc_operand<BK>(sB(s), B_MN, kMnLbo);
+          const uint64_t dal = smem_desc_operand<BK>(sAlo(s), A_MN, kMnLbo);
+          const uint64_t dbl = smem_desc_operand<BK>(sBlo(s), B_MN, kMnLbo);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t aa = uint64_t((k * kAStep) >> 4);  // byte offset >> 4 into the address field
@@ -507,16 +517,18 @@ EncodeFn get_encode() {
 // 128-byte swizzle; MN-major operands pass (rows = K, cols = M or N) and take
 // the 32-byte-atom one.
 int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows,
-             bool mn_major) {
+             bool mn_major, int bk) {
   EncodeFn enc = get_encode();
   if (!enc) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
   cuuint64_t strides[1] = {cuuint64_t(ld) * 4};
-  cuuint32_t box[2] = {32u, cuuint32_t(box_rows)};
+  // MN-major: 32 columns (128 bytes) x bk rows; K-major: bk columns x box_rows rows
+  cuuint32_t box[2] = {mn_major ? 32u : cuuint32_t(bk), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                            : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
@@ -567,7 +579,8 @@ Plan make_plan(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int passes) {
   pl.conv_b = pl.b_mn || !(small_b);
   if (passes != 3) pl.conv_b = pl.b_mn;  // selects the template only
   const int64_t tiles = gc::ceil_div(M, BM) * gc::ceil_div(N, pl.bn);
-  const int64_t nkb = gc::ceil_div(K, BK);
+  const int bk = (passes == 3 && pl.bn == 256) ? 16 : 32;
+  const int64_t nkb = gc::ceil_div(K, bk);
   int64_t splits = 1;
   if (tiles * 2 <= gc::kNumSMs && nkb >= 64) splits = std::min<int64_t>(gc::kNumSMs / tiles, nkb / 16);
   splits = std::max<int64_t>(1, splits);
@@ -678,14 +691,15 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
   if (!aligned16(Aop) || !aligned16(Bop)) return fail(GC_ERR_UNSUPPORTED, "gemm_tc: operand base not 16-byte aligned");
 
   CUtensorMap mA, mB, mBlo;
-  if (pl.a_mn) rc = make_map(&mA, Aop, K, M, lda_op, BK, true);
-  else rc = make_map(&mA, Aop, M, K, lda_op, BM, false);
+  const int bk = (passes == 3 && pl.bn == 256) ? 16 : 32;
+  if (pl.a_mn) rc = make_map(&mA, Aop, K, M, lda_op, bk, true, bk);
+  else rc = make_map(&mA, Aop, M, K, lda_op, BM, false, bk);
   if (rc != GC_OK) return rc;
-  if (pl.b_mn) rc = make_map(&mB, Bop, K, N, ldb_op, BK, true);
-  else rc = make_map(&mB, Bop, N, K, ldb_op, pl.bn, false);
+  if (pl.b_mn) rc = make_map(&mB, Bop, K, N, ldb_op, bk, true, bk);
+  else rc = make_map(&mB, Bop, N, K, ldb_op, pl.bn, false, bk);
   if (rc != GC_OK) return rc;
   if (pl.b_mn) mBlo = mB;
-  else if ((rc = make_map(&mBlo, Blo, N, K, ldblo, pl.bn, false)) != GC_OK) return rc;
+  else if ((rc = make_map(&mBlo, Blo, N, K, ldblo, pl.bn, false, bk)) != GC_OK) return rc;
 
   TcParams p;
   p.M = int(M);

@@ -13,8 +13,9 @@
 //     panel boundaries (panel = a range of columns whose rows of H fit the
 //     L2 together); pieces are processed panel by panel, so the whole GPU
 //     gathers from one L2-resident slab of H at a time;
-//   * any piece longer than GC_SPMM_SEGMENT is cut further, so a hub row is
-//     spread over many warps;
+//   * any piece longer than the plan's segment length (128..2048 non-zeros,
+//     growing with the size of the matrix) is cut further, so a hub row is
+//     spread over many warps and no single piece dominates the launch;
 //   * pieces of cut rows write partial sums to scratch; a finalize pass adds
 //     a row's partials in piece order and applies the epilogue -- no atomics
 //     anywhere, results are bit-reproducible run to run;
@@ -255,12 +256,12 @@ __device__ __forceinline__ int lower_bound_col(const int32_t* __restrict__ col, 
   return lo;
 }
 
-__device__ __forceinline__ int pieces_of(int cnt) { return (cnt + GC_SPMM_SEGMENT - 1) / GC_SPMM_SEGMENT; }
+__device__ __forceinline__ int pieces_of(int cnt, int seg) { return (cnt + seg - 1) / seg; }
 
 // Per row: how many pieces it contributes and whether it is cut.
 __global__ void __launch_bounds__(256)
 plan_count_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col, int M, int K, int panel_cols,
-                  int32_t* __restrict__ rows_pieces, int32_t* __restrict__ rows_cut,
+                  int seg, int32_t* __restrict__ rows_pieces, int32_t* __restrict__ rows_cut,
                   int32_t* __restrict__ rows_slots) {
   const int r = blockIdx.x * 256 + threadIdx.x;
   if (r >= M) return;
@@ -272,11 +273,11 @@ plan_count_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict_
     int lo = s;
     for (int p = 0; p < n_panels && lo < e; ++p) {
       const int hi = (p + 1 == n_panels) ? e : lower_bound_col(col, lo, e, (p + 1) * panel_cols);
-      pieces += pieces_of(hi - lo);
+      pieces += pieces_of(hi - lo, seg);
       lo = hi;
     }
   } else {
-    pieces = max(1, pieces_of(d));
+    pieces = max(1, pieces_of(d, seg));
   }
   rows_pieces[r] = pieces;
   rows_cut[r] = pieces > 1 ? 1 : 0;
@@ -299,7 +300,7 @@ __global__ void plan_totals_kernel(const int32_t* __restrict__ rows_pieces, cons
 // only, n_panels for uncut rows (they run after all panels).
 __global__ void __launch_bounds__(256)
 plan_emit_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col, int M, int K, int panel_cols,
-                 const int32_t* __restrict__ rows_cut, const int32_t* __restrict__ piece_base,
+                 int seg, const int32_t* __restrict__ rows_cut, const int32_t* __restrict__ piece_base,
                  const int32_t* __restrict__ cut_base, const int32_t* __restrict__ slot_base,
                  const int32_t* __restrict__ rows_pieces, uint64_t* __restrict__ keys, int32_t* __restrict__ ids,
                  int32_t* __restrict__ u_start, int32_t* __restrict__ u_len, int32_t* __restrict__ u_target,
@@ -326,8 +327,8 @@ plan_emit_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__
   int lo = s;
   for (int p = 0; p < (by_panel ? n_panels : 1) && lo < e; ++p) {
     const int hi = (!by_panel || p + 1 == n_panels) ? e : lower_bound_col(col, lo, e, (p + 1) * panel_cols);
-    for (int q = lo; q < hi; q += GC_SPMM_SEGMENT) {
-      const int len = min(GC_SPMM_SEGMENT, hi - q);
+    for (int q = lo; q < hi; q += seg) {
+      const int len = min(seg, hi - q);
       u_start[out] = q;
       u_len[out] = len;
       u_target[out] = ~slot;
@@ -422,10 +423,10 @@ int exclusive_scan(const PlanWs& w, const int32_t* in, int32_t* out, int n, cuda
   return GC_OK;
 }
 
-int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int panel_cols, const PlanWs& w,
+int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int panel_cols, int seg, const PlanWs& w,
                cudaStream_t st) {
   const unsigned g = unsigned((M + 255) / 256);
-  plan_count_kernel<<<g, 256, 0, st>>>(rowptr, col, M, K, panel_cols, w.rows_pieces, w.rows_cut, w.rows_slots);
+  plan_count_kernel<<<g, 256, 0, st>>>(rowptr, col, M, K, panel_cols, seg, w.rows_pieces, w.rows_cut, w.rows_slots);
   int rc = gc::check_launch("spmm plan: count");
   if (rc == GC_OK) rc = exclusive_scan(w, w.rows_pieces, w.piece_base, M, st);
   if (rc == GC_OK) rc = exclusive_scan(w, w.rows_cut, w.cut_base, M, st);
@@ -501,15 +502,26 @@ int64_t gc_spmm_default_panel_cols(int64_t K, int64_t F) {
   return std::min<int64_t>(p2, std::max<int64_t>(K, 1));
 }
 
+int64_t gc_spmm_default_segment(int64_t nnz) {
+  // A piece is walked by one group of lanes, a few gathers per memory round
+  // trip, so its length bounds the critical path of the launch.  Aim at about
+  // twice the average load of the ~16 K groups a B200 keeps resident.
+  int64_t want = nnz / 8192;
+  int64_t p2 = 128;
+  while (p2 < want && p2 < GC_SPMM_SEGMENT_MAX) p2 *= 2;
+  return p2;
+}
+
 size_t gc_spmm_plan_workspace_bytes(int64_t M, int64_t n_pieces) {
   if (M < 0 || n_pieces < 0) return 0;
   return carve(nullptr, M, n_pieces).total;
 }
 
 int gc_spmm_plan_count(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
-                       int64_t* counts, void* workspace, size_t workspace_bytes, void* stream) {
+                       int64_t segment, int64_t* counts, void* workspace, size_t workspace_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && M < INT32_MAX && K < INT32_MAX, "gc_spmm_plan_count: size out of int32 range");
   GC_REQUIRE(panel_cols >= 1 && panel_cols < INT32_MAX, "gc_spmm_plan_count: panel_cols must be positive");
+  GC_REQUIRE(segment >= 32 && segment <= GC_SPMM_SEGMENT_MAX, "gc_spmm_plan_count: segment out of range");
   GC_REQUIRE(counts && workspace, "gc_spmm_plan_count: null pointer");
   GC_REQUIRE(M == 0 || rowptr, "gc_spmm_plan_count: null rowptr");
   if (workspace_bytes < gc_spmm_plan_workspace_bytes(M, 0))
@@ -517,7 +529,7 @@ int gc_spmm_plan_count(const int32_t* rowptr, const int32_t* col, int64_t M, int
   cudaStream_t st = gc::as_stream(stream);
   const PlanWs w = carve(workspace, M, 0);
   if (M > 0) {
-    int rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), w, st);
+    int rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), int(segment), w, st);
     if (rc != GC_OK) return rc;
   }
   plan_totals_kernel<<<1, 1, 0, st>>>(w.rows_pieces, w.rows_cut, w.rows_slots, w.piece_base, w.cut_base,
@@ -531,10 +543,11 @@ size_t gc_spmm_plan_bytes(int64_t n_pieces, int64_t n_cut) {
 }
 
 int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
-                       int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
+                       int64_t segment, int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
                        void* workspace, size_t workspace_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && M < INT32_MAX && K < INT32_MAX, "gc_spmm_plan_build: size out of int32 range");
   GC_REQUIRE(panel_cols >= 1 && panel_cols < INT32_MAX, "gc_spmm_plan_build: panel_cols must be positive");
+  GC_REQUIRE(segment >= 32 && segment <= GC_SPMM_SEGMENT_MAX, "gc_spmm_plan_build: segment out of range");
   GC_REQUIRE(n_pieces >= M && n_pieces < INT32_MAX && n_slots >= 0 && n_slots < INT32_MAX && n_cut >= 0 && n_cut <= M,
              "gc_spmm_plan_build: counts are not those gc_spmm_plan_count reported");
   GC_REQUIRE(plan && workspace, "gc_spmm_plan_build: null pointer");
@@ -549,9 +562,9 @@ int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int
   plan_header_kernel<<<1, 1, 0, st>>>(pv.hdr, int(M), int(n_pieces), int(n_slots), int(n_cut), int(panel_cols));
   int rc = gc::check_launch("spmm plan: header");
   if (rc != GC_OK || M == 0) return rc;
-  if ((rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), w, st)) != GC_OK) return rc;
+  if ((rc = count_rows(rowptr, col, int(M), int(K), int(panel_cols), int(segment), w, st)) != GC_OK) return rc;
   const unsigned gm = unsigned((M + 255) / 256), gp = unsigned((n_pieces + 255) / 256);
-  plan_emit_kernel<<<gm, 256, 0, st>>>(rowptr, col, int(M), int(K), int(panel_cols), w.rows_cut, w.piece_base,
+  plan_emit_kernel<<<gm, 256, 0, st>>>(rowptr, col, int(M), int(K), int(panel_cols), int(segment), w.rows_cut, w.piece_base,
                                        w.cut_base, w.slot_base, w.rows_pieces, w.keys, w.ids, w.u_start, w.u_len,
                                        w.u_target, pv.cut_row, pv.cut_slot0, pv.cut_nslots);
   if ((rc = gc::check_launch("spmm plan: emit")) != GC_OK) return rc;

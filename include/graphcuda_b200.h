@@ -58,8 +58,8 @@ const char* gc_status_string(int status);
  *     panel boundaries (panel_cols columns per panel) and the pieces are
  *     processed panel by panel, so the gathers of a phase hit one slab of H
  *     that stays in the L2;
- *   - pieces longer than GC_SPMM_SEGMENT are cut further, so heavy rows are
- *     spread over many warps;
+ *   - pieces longer than `segment` non-zeros are cut further, so heavy rows are
+ *     spread over many warps and no piece dominates the launch;
  *   - within a phase pieces are ordered by decreasing length.
  * Pieces of cut rows write partial sums ("slots") to scratch; a second pass
  * adds them in a fixed order.  Building is two calls because the sizes depend
@@ -67,20 +67,23 @@ const char* gc_status_string(int status);
  * gc_spmm_plan_build.
  */
 #define GC_SPMM_PANEL_MIN_ROW 128 /* rows with more non-zeros than this are cut at panel boundaries */
-#define GC_SPMM_SEGMENT 2048      /* longest piece, in non-zeros */
+#define GC_SPMM_SEGMENT_MAX 2048  /* upper limit of the segment length, in non-zeros */
 
 /* Default panel width (columns): a power of two for which panel_cols rows of H
  * (F fp32 each) take about 128 MB, at most 262144 and at most K. */
 int64_t gc_spmm_default_panel_cols(int64_t K, int64_t F);
+/* Default segment length for a matrix of nnz non-zeros: a power of two in
+ * [128, GC_SPMM_SEGMENT_MAX], about nnz / 8192. */
+int64_t gc_spmm_default_segment(int64_t nnz);
 /* Scratch for plan construction; pass n_pieces = 0 for gc_spmm_plan_count. */
 size_t gc_spmm_plan_workspace_bytes(int64_t M, int64_t n_pieces);
 /* counts (device, int64[3]) <- {n_pieces, n_slots, n_cut}. */
 int gc_spmm_plan_count(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
-                       int64_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+                       int64_t segment, int64_t* counts, void* workspace, size_t workspace_bytes, void* stream);
 size_t gc_spmm_plan_bytes(int64_t n_pieces, int64_t n_cut);
 /* plan: 16-byte aligned device memory of gc_spmm_plan_bytes(n_pieces, n_cut). */
 int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int64_t K, int64_t panel_cols,
-                       int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
+                       int64_t segment, int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* plan, size_t plan_bytes,
                        void* workspace, size_t workspace_bytes, void* stream);
 /* Scratch gc_spmm_csr_f32 needs with a plan of n_slots slots and F feature columns. */
 size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F);

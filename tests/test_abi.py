@@ -76,6 +76,10 @@ def test_plan_and_workspace_sizes():
     assert L.gc_spmm_default_panel_cols(2_449_029, 256) == 131072
     assert L.gc_spmm_default_panel_cols(2_449_029, 48) == 262144
     assert L.gc_spmm_default_panel_cols(2708, 16) == 2708
+    # segment length: a power of two near nnz / 8192 within [128, 2048]
+    assert L.gc_spmm_default_segment(13_566) == 128
+    assert L.gc_spmm_default_segment(2_501_829) == 512
+    assert L.gc_spmm_default_segment(126_167_309) == 2048
     assert L.gc_gemm_workspace_bytes(0, 0, 4096, 256, 256, _lib.PREC_TF32X3) >= 256 + 2 * 256 * 256 * 4
 
 

@@ -27,19 +27,27 @@ def test_feature_widths(cuda, F):
 
 @pytest.mark.parametrize("F", [16, 100, 256])
 def test_long_rows_are_cut_into_pieces(cuda, F):
-    # rows of about 1500, 2048, 2049 and 9000 non-zeros: cut at 2048 (one panel: H fits the L2)
+    # rows of about 1500, 2048, 2049 and 9000 non-zeros, cut every `seg` non-zeros (one panel: H fits the L2)
     A = random_csr(3000, 12000, 4.0, seed=3, long_rows=((7, 1500), (100, 2048), (101, 2049), (2999, 9000)))
     H = torch.randn(12000, F, generator=torch.Generator().manual_seed(9))
     ref = O.spmm(A, H)
     adj = to_gpu_csr(A, cuda)
+    from graphcuda_b200 import _lib
+    seg = int(_lib.lib().gc_spmm_default_segment(adj.nnz))
+    assert seg == 128  # a small matrix gets short pieces
     deg = (adj.rowptr[1:] - adj.rowptr[:-1]).cpu()
-    pieces_per_row = torch.clamp((deg + 2047) // 2048, min=1)
+    pieces_per_row = torch.clamp((deg + seg - 1) // seg, min=1)
     n_pieces, n_slots, n_cut = adj.plan_counts(F)
     assert n_pieces == int(pieces_per_row.sum())
-    assert n_cut == int((pieces_per_row > 1).sum()) and n_cut >= 2
+    assert n_cut == int((pieces_per_row > 1).sum()) and n_cut >= 4
     assert n_slots == int(pieces_per_row[pieces_per_row > 1].sum())
     out = adj.matmul(H.to(cuda))
     assert O.rel_fro(out, ref) < TOL and O.rel_max(out, ref) < TOL
+    # the longest allowed pieces give the same product
+    long_seg = to_gpu_csr(A, cuda)
+    long_seg.segment = 2048
+    assert long_seg.plan_counts(F)[0] < n_pieces
+    assert O.rel_fro(long_seg.matmul(H.to(cuda)), ref) < TOL
     # same result without a plan (every row one piece, natural order)
     from graphcuda_b200 import CSRAdjacency
     plain = CSRAdjacency(adj.rowptr, adj.col, adj.val, adj.shape, build_plan=False)
