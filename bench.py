@@ -516,6 +516,15 @@ def aux_measurements(dev, args):
             "gbs_l2_flushed": nbytes / (ms_cold * 1e-3) / 1e9, "frac_hbm_l2_flushed": nbytes / (ms_cold * 1e-3) / 1e9 / peak,
             "gbs_l2_warm": nbytes / (ms_warm * 1e-3) / 1e9,
         }
+    # same-box library context: cuSPARSE through torch.sparse.mm on the same matrix (what the reference's
+    # spmm_cusparse wrapper calls, src/graphcuda/cuda/spmm_cusparse.cu:105-116, there in COO form)
+    try:
+        A_csr = torch.sparse_csr_tensor(adj.rowptr.long(), adj.col.long(), adj.val, size=adj.shape)
+        Hc = synth.normal_features(c["nodes"], 256, seed=256, device=dev)
+        out["arxiv_like_spmm_F256_cusparse_via_torch_ms"] = _time_ms(lambda: torch.sparse.mm(A_csr, Hc))
+        del A_csr, Hc
+    except Exception as ex:
+        out["arxiv_like_spmm_F256_cusparse_via_torch_ms"] = repr(ex)
     # feature transform 169,343 x 128 x 256 on the tensor cores (split-TF32) vs CUDA cores
     Xa = synth.normal_features(c["nodes"], 128, seed=3, device=dev)
     W = synth.reference_init(128, 256, seed=4, device=dev)
@@ -525,6 +534,56 @@ def aux_measurements(dev, args):
         ms = _time_ms(lambda: gc.gemm(Xa, W, precision=prec))
         out[f"arxiv_like_gemm_{prec}"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
                                           "gbs": gbytes / (ms * 1e-3) / 1e9, "frac_hbm": gbytes / (ms * 1e-3) / 1e9 / peak}
+    del Xa, adj, e
+
+    # GEMM operator sweep (matmul1..4 / gemm_cublas all run this engine): uniform(-1, 1) operands
+    sweep = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    for (M, N, K) in ((2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (1 << 20, 64, 128),
+                      (1 << 20, 256, 256)):
+        A = torch.rand(M, K, generator=g, device=dev) * 2 - 1
+        B = torch.rand(K, N, generator=g, device=dev) * 2 - 1
+        fl = 2.0 * M * N * K
+        by = 4.0 * (M * K + K * N + M * N)
+        row = {}
+        for prec in ("tf32x3", "tf32"):
+            ms = _time_ms(lambda: gc.gemm(A, B, precision=prec), warm=2, iters=5)
+            row[prec] = {"ms": ms, "useful_tflops": fl / (ms * 1e-3) / 1e12, "gbs": by / (ms * 1e-3) / 1e9}
+        # same-box library context: cuBLAS SGEMM through torch.matmul (fp32, TF32 off), what the reference's
+        # gemm_cublas wrapper calls (src/graphcuda/cuda/gemm_cublas.cu:37-48)
+        torch.backends.cuda.matmul.allow_tf32 = False
+        ms = _time_ms(lambda: torch.matmul(A, B), warm=2, iters=5)
+        row["cublas_sgemm_via_torch"] = {"ms": ms, "useful_tflops": fl / (ms * 1e-3) / 1e12}
+        sweep[f"{M}x{N}x{K}"] = row
+        del A, B
+    out["gemm_sweep"] = sweep
+
+    # dense-adjacency fused aggregation: N = 32,768, G(n, p = 0.01) + self-loops, normalised, dense fp32 (4.3 GB);
+    # Y = relu(A_hat (X W) + b), 512 -> 256
+    n4 = 32768
+    e4 = synth.erdos_renyi_edges(n4, 0.01, seed=3, device=dev)
+    a4 = gc.normalized_adjacency(synth.symmetrize(e4), n4, symmetric=True)
+    dense = torch.zeros(n4, n4, device=dev)
+    rows4 = torch.repeat_interleave(torch.arange(n4, device=dev), (a4.rowptr[1:] - a4.rowptr[:-1]).long())
+    dense[rows4, a4.col.long()] = a4.val
+    X4 = synth.normal_features(n4, 512, seed=5, device=dev)
+    W4 = synth.reference_init(512, 256, seed=6, device=dev)
+    b4 = synth.normal_features(1, 256, seed=7, device=dev)[0] * 0.1
+    dadj = gc.DenseAdjacency(dense, symmetric=True)
+    fl4 = 2.0 * n4 * 512 * 256 + 2.0 * n4 * n4 * 256
+    row = {}
+    for prec in ("tf32x3", "tf32"):
+        def fused():
+            H = gc.gemm(X4, W4, precision=prec)
+            return dadj.matmul(H, bias=b4, relu=True, precision=prec)
+        ms = _time_ms(fused, warm=2, iters=5)
+        row[prec] = {"ms": ms, "useful_tflops": fl4 / (ms * 1e-3) / 1e12,
+                     "adj_gbs": 4.0 * n4 * n4 / (ms * 1e-3) / 1e9}
+    # the same layer through the CSR path
+    ms = _time_ms(lambda: a4.matmul(gc.gemm(X4, W4), bias=b4, relu=True), warm=2, iters=5)
+    row["csr"] = {"ms": ms}
+    out["dense_adj_32768_512_256"] = row
     return out
 
 
