@@ -51,6 +51,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary single-GPU measurements")
     ap.add_argument("--cpu-sample-div", type=int, default=32)
+    ap.add_argument("--partition", default="auto", choices=["auto", "features", "rows"],
+                    help="multi-GPU scheme: aggregation sharded over feature columns (all-to-all) or adjacency rows "
+                         "(all-gather); auto = rows up to 4 GPUs, features from 8 (measured cross-over)")
     ap.add_argument("--profile-warmup", action="store_true",
                     help="honour --warmup below 3 (profiler captures only; such a run is not a benchmark)")
     return ap.parse_args()
@@ -247,7 +250,7 @@ def config_dict(cfg, args, world):
         "workload": "rmat_products: 3-layer GCN 100-256-256-47 train step, R-MAT a=.57 b=.19 c=.19 d=.05",
         "nodes": cfg["nodes"], "undirected_edges": cfg["edges"], "nnz": 2 * cfg["edges"] + cfg["nodes"],
         "dims": DIMS, "optimizer": "Adam lr=0.01", "loss": "nll over all nodes",
-        "parallelism": f"row-partition x{world}" if world > 1 else "single GPU",
+        "parallelism": (f"{args.partition}-sharded x{world}" if world > 1 else "single GPU"),
         "precision": args.precision, "l2": "inputs larger than L2 (no flush needed)",
         "shrink": args.shrink,
     }
@@ -260,11 +263,13 @@ def run_ours(args):
     import graphcuda_b200 as gc
     from graphcuda_b200 import _lib, adjacency, ops, synth
     from graphcuda_b200.models import GCN
-    from graphcuda_b200.partition import DistGCN, PartitionedGraph
+    from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, PartitionedGraph, RowPartition
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.partition == "auto":
+        args.partition = "features" if world >= 8 else "rows"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local)
@@ -289,13 +294,18 @@ def run_ours(args):
         model = GCN(DIMS, precision=args.precision).to(dev)
         rows = n
     else:
-        part = PartitionedGraph(adj.rowptr, adj.col, adj.val, n, rank=rank, world=world)
+        if args.partition == "rows":
+            part = PartitionedGraph(adj.rowptr, adj.col, adj.val, n, rank=rank, world=world)
+        else:
+            part = FeatureShardedGraph(adj, n, rank=rank, world=world)
         lo, hi = part.lo, part.hi
         Xf = synth.normal_features(n, DIMS[0], seed=11, device=dev)
         yf = synth.uniform_labels(n, DIMS[-1], seed=12, device=dev)
         X = Xf[lo:hi].contiguous()
         y = yf[lo:hi].contiguous()
-        del Xf, yf, adj
+        del Xf, yf
+        if args.partition == "rows":
+            del adj
         torch.manual_seed(0)
         model = DistGCN(DIMS, precision=args.precision).to(dev)
         rows = hi - lo
@@ -306,10 +316,7 @@ def run_ours(args):
 
     X_gathered = None
     if world > 1:
-        X_gathered, w = part.all_gather_rows_async(X, tag="x")
-        if w is not None:
-            w.wait()
-        X_gathered = X_gathered.clone()
+        X_gathered = part.prepare_constant(X)
 
     def step(Xd, yd, Xg):
         opt.zero_grad(set_to_none=True)
@@ -373,11 +380,7 @@ def run_ours(args):
     def e2e_step():
         Xd.copy_(Xh, non_blocking=True)
         yd.copy_(yh, non_blocking=True)
-        Xg = None
-        if world > 1:
-            Xg, w = part.all_gather_rows_async(Xd, tag="x")
-            if w is not None:
-                w.wait()
+        Xg = part.prepare_constant(Xd) if world > 1 else None
         return float(step(Xd, yd, Xg).item())  # .item() is the device-to-host read of the result
 
     for _ in range(2):

@@ -10,8 +10,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from graphcuda_b200.partition import (DistGCN, PartitionedGraph, RowPartition, slice_csr_rows,
-                                      split_csr_columns)
+from graphcuda_b200.partition import (DistGCN, FeatureShardedGraph, PartitionedGraph, RowPartition,
+                                      slice_csr_rows, split_csr_columns)
 from oracle import gcn_oracle as O
 
 
@@ -21,7 +21,7 @@ class TorchCPUBackend:
     def make_adj(self, rowptr, col, val, shape):
         return torch.sparse_csr_tensor(rowptr.long(), col.long(), val, size=tuple(shape))
 
-    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None):
+    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
         y = adj @ H if adj.shape[0] and adj.shape[1] else torch.zeros(adj.shape[0], H.size(1))
         if accumulate_into is not None:
             y = accumulate_into + y
@@ -32,6 +32,9 @@ class TorchCPUBackend:
         if accumulate_into is not None:  # in place, like the CUDA kernel
             accumulate_into.copy_(y)
             return accumulate_into
+        if out is not None:
+            out.copy_(y)
+            return out
         return y
 
     def gemm(self, A, B, *, bias=None, relu=False, precision=None):
@@ -91,7 +94,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, n, dims, q):
+def _worker(rank, world, port, n, dims, q, mode="rows"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -101,15 +104,17 @@ def _worker(rank, world, port, n, dims, q):
         g = torch.Generator().manual_seed(0)
         X = torch.randn(n, dims[0], generator=g)
         y = torch.randint(0, dims[-1], (n,), generator=g)
-        graph = PartitionedGraph(rowptr, col, val, n, backend=TorchCPUBackend())
+        be = TorchCPUBackend()
+        if mode == "rows":
+            graph = PartitionedGraph(rowptr, col, val, n, backend=be)
+        else:
+            graph = FeatureShardedGraph(be.make_adj(rowptr, col, val, (n, n)), n, backend=be)
         lo, hi = graph.lo, graph.hi
         torch.manual_seed(5)
         model = DistGCN(dims)
         Xl = X[lo:hi].clone().requires_grad_()
-        # constant input features: gathered once, outside the step
-        Xg, work = graph.all_gather_rows_async(X[lo:hi], tag="x")
-        if work is not None:
-            work.wait()
+        # constant input features: exchanged once, outside the step
+        Xg = graph.prepare_constant(X[lo:hi])
         out = model(Xl, graph, X_gathered=Xg)
         loss = torch.nn.functional.nll_loss(out, y[lo:hi], reduction="sum") / n
         loss.backward()
@@ -121,11 +126,12 @@ def _worker(rank, world, port, n, dims, q):
 
 
 @pytest.mark.parametrize("world,n,dims", [(2, 64, [12, 20, 20, 5]), (3, 50, [9, 16, 4]), (2, 33, [20, 8, 6])])
-def test_partitioned_model_matches_single_process(world, n, dims):
+@pytest.mark.parametrize("mode", ["rows", "features"])
+def test_partitioned_model_matches_single_process(world, n, dims, mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]

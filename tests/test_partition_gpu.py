@@ -31,7 +31,7 @@ def _inputs(n, dims):
     return A, X, y
 
 
-def _worker(rank, world, port, n, dims, q):
+def _worker(rank, world, port, n, dims, q, mode):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -39,17 +39,19 @@ def _worker(rank, world, port, n, dims, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        from graphcuda_b200.partition import DistGCN, PartitionedGraph
+        from graphcuda_b200 import CSRAdjacency
+        from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, PartitionedGraph
         A, X, y = _inputs(n, dims)
         rowptr, col, val = O.coo_to_csr_int32(A)
-        graph = PartitionedGraph(rowptr.to(dev), col.to(dev), val.to(dev), n)
+        if mode == "rows":
+            graph = PartitionedGraph(rowptr.to(dev), col.to(dev), val.to(dev), n)
+        else:
+            graph = FeatureShardedGraph(CSRAdjacency(rowptr.to(dev), col.to(dev), val.to(dev), (n, n)), n)
         lo, hi = graph.lo, graph.hi
         torch.manual_seed(5)
         model = DistGCN(dims).to(dev)
         Xl = X[lo:hi].to(dev).requires_grad_()
-        Xg, work = graph.all_gather_rows_async(Xl.detach(), tag="x")
-        if work is not None:
-            work.wait()
+        Xg = graph.prepare_constant(Xl.detach())
         out = model(Xl, graph, X_gathered=Xg)
         loss = torch.nn.functional.nll_loss(out, y[lo:hi].to(dev), reduction="sum") / n
         loss.backward()
@@ -61,14 +63,15 @@ def _worker(rank, world, port, n, dims, q):
 
 
 @pytest.mark.parametrize("n,dims", [(5000, [24, 32, 32, 7]), (3001, [40, 16, 5]), (4000, [24, 128, 256, 7])])
-def test_two_gpu_partition_matches_oracle(n, dims):
+@pytest.mark.parametrize("mode", ["rows", "features"])
+def test_two_gpu_partition_matches_oracle(n, dims, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in range(world)]
