@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-4  # relative Frobenius / max, fp32 path
 
 
-@pytest.mark.parametrize("F", [1, 3, 7, 8, 16, 47, 48, 64, 100, 128, 200, 256, 260, 700])
+@pytest.mark.parametrize("F", [1, 3, 4, 7, 8, 12, 16, 20, 28, 32, 36, 47, 48, 64, 100, 128, 200, 256, 260, 700])
 def test_feature_widths(cuda, F):
     A = random_csr(500, 400, 9.0, seed=F, empty_rows=(0, 13, 499))
     H = torch.randn(400, F, generator=torch.Generator().manual_seed(F + 1))
