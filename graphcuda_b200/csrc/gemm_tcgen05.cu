@@ -183,7 +183,10 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kABytes + kBBytes);
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStagingBytes = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 tile per epilogue warp
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStagingBytes;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static_assert(kStages >= 2, "need at least two stages");
 };
@@ -216,6 +219,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   auto bar_conv = [&](int s) { return bars + 8 * (2 * S + s); };
   auto bar_tfull = [&](int b) { return bars + 8 * (3 * S + b); };
   auto bar_tempty = [&](int b) { return bars + 8 * (3 * S + 2 + b); };
+  float* stage_tiles = reinterpret_cast<float*>(smem + S * C_::kStageBytes + 256);
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -380,32 +384,44 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             const int gn = gn0 + j;
             if (gn < p.N && gm < p.M) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
           }
-        } else if (gm < p.M) {
-          if (vec && gn0 + 32 <= p.N) {
-            float* crow = Cb + int64_t(gm) * ldc + gn0;
-            float* mrow = ep.mask ? ep.mask + int64_t(gm) * ldc + gn0 : nullptr;
+        } else if (vec && gn0 + 32 <= p.N) {
+          // The accumulator arrives one row per lane.  Stored like that, every
+          // 128-bit store of the warp would touch 32 different lines (half a
+          // sector each).  The 32 x 32 block is turned through shared memory
+          // (pitch 33: conflict-free both ways) so that each store covers four
+          // complete 128-byte row segments.
+          float* tile = stage_tiles + (warp - 4) * (32 * 33);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                     __uint_as_float(r[j + 3]));
+          for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(r[j]);
+          __syncwarp();
+          const int c4 = (lane % 8) * 4;
+#pragma unroll
+          for (int pass = 0; pass < 8; ++pass) {
+            const int row = pass * 4 + lane / 8;
+            const int gmr = m0 + q * 32 + row;
+            const float* tp = tile + row * 33 + c4;
+            float4 v = make_float4(tp[0], tp[1], tp[2], tp[3]);
+            if (gmr < p.M) {
+              float* cptr = Cb + int64_t(gmr) * ldc + gn0 + c4;
               if (ep.bias) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + j));
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + c4));
                 v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
               }
-              if (ep.relu || mrow) {
+              if (ep.relu || ep.mask) {
                 const float4 mk = make_float4(v.x > 0.f ? 1.f : 0.f, v.y > 0.f ? 1.f : 0.f, v.z > 0.f ? 1.f : 0.f,
                                               v.w > 0.f ? 1.f : 0.f);
-                if (mrow) *reinterpret_cast<float4*>(mrow + j) = mk;
+                if (ep.mask) *reinterpret_cast<float4*>(ep.mask + int64_t(gmr) * ldc + gn0 + c4) = mk;
                 if (ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
               }
-              *reinterpret_cast<float4*>(crow + j) = v;
+              *reinterpret_cast<float4*>(cptr) = v;
             }
-          } else {
+          }
+          __syncwarp();
+        } else if (gm < p.M) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int gn = gn0 + j;
-              if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
-            }
+          for (int j = 0; j < 32; ++j) {
+            const int gn = gn0 + j;
+            if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
           }
         }
       }
