@@ -305,11 +305,15 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
     if (lane_g == a && a < units) finish_store<4>(acc[a], yrow, mrow, a * 4, my_ep);
 }
 
-// One warp per cut row: adds that row's partial sums in slot order, then the fused store.
+// One warp per cut row: adds that row's partial sums in slot order, then the
+// fused store.  Lanes cover the feature columns (128-bit vectors when the rows
+// are aligned); four slots are loaded ahead of the ordered additions.
+template <int VW>
 __global__ void __launch_bounds__(256)
 spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, const int32_t* __restrict__ cut_slot0,
                      const int32_t* __restrict__ cut_nslots, const float* __restrict__ scratch, int64_t ldS,
                      int slot_capacity, float* __restrict__ Y, int64_t ldY, Epilogue ep) {
+  using V = Vec<VW>;
   const int lane = threadIdx.x % 32;
   const int warps = gridDim.x * 8;
   for (int i = blockIdx.x * 8 + threadIdx.x / 32; i < n_cut; i += warps) {
@@ -318,10 +322,17 @@ spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, cons
     const int s1 = min(s0 + __ldg(cut_nslots + i), slot_capacity);
     float* yrow = Y + int64_t(row) * ldY;
     float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
-    for (int f = lane; f < F; f += 32) {
-      float s = 0.f;
-      for (int sl = s0; sl < s1; ++sl) s += scratch[int64_t(sl) * ldS + f];
-      finish_store<1>(s, yrow, mrow, f, ep);
+    for (int f = lane * VW; f < F; f += 32 * VW) {
+      typename V::T s = V::zero();
+      int sl = s0;
+      for (; sl + 4 <= s1; sl += 4) {
+        const float* p = scratch + int64_t(sl) * ldS + f;
+        const typename V::T a = V::load_plain(p), b = V::load_plain(p + ldS), c = V::load_plain(p + 2 * ldS),
+                            d = V::load_plain(p + 3 * ldS);
+        s = V::add(V::add(V::add(V::add(s, a), b), c), d);
+      }
+      for (; sl < s1; ++sl) s = V::add(s, V::load_plain(scratch + int64_t(sl) * ldS + f));
+      finish_store<VW>(s, yrow, mrow, f, ep);
     }
   }
 }
@@ -736,8 +747,12 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
   if (rc != GC_OK) return rc;
   if (planned && n_cut > 0) {
     const unsigned g = unsigned(std::min<int64_t>((n_cut + 7) / 8, gc::kNumSMs * 8));
-    spmm_finalize_kernel<<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
-                                            cap, Y, ldY, ep);
+    if (vec4)
+      spmm_finalize_kernel<4><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
+                                                 cap, Y, ldY, ep);
+    else
+      spmm_finalize_kernel<1><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
+                                                 cap, Y, ldY, ep);
     rc = gc::check_launch("gc_spmm_csr_f32 (finalize)");
   }
   return rc;
