@@ -110,8 +110,10 @@ class CSRAdjacency:
     # -- products -----------------------------------------------------------
     def matmul(self, H: torch.Tensor, *, bias: Optional[torch.Tensor] = None, relu: bool = False,
                want_mask: bool = False, accumulate_into: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None, panel_cols: Optional[int] = None):
-        """Y = A @ H (+bias)(ReLU).  Returns Y or (Y, mask)."""
+               out: Optional[torch.Tensor] = None, panel_cols: Optional[int] = None,
+               gate: Optional[torch.Tensor] = None):
+        """Y = A @ H (+bias)(ReLU).  Returns Y or (Y, mask).  gate (contiguous,
+        shape of Y): Y is multiplied by (gate > 0) in the store."""
         _require(H.dim() == 2, "B must be 2D")
         _require(H.size(0) == self.shape[1], "A.cols must match B.rows")
         _require(H.is_cuda and H.device == self.device, "A and B must be CUDA tensors on the same device")
@@ -136,6 +138,9 @@ class CSRAdjacency:
         if bias is not None:
             _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == F, "bias must be float32 [F]")
             bias = bias.contiguous()
+        if gate is not None:
+            _require(gate.is_cuda and gate.dtype == torch.float32 and tuple(gate.shape) == (M, F)
+                     and gate.is_contiguous() and ldy == F, "gate must be a contiguous float32 tensor of Y's shape")
         if M == 0 or F == 0:
             return (out, mask) if want_mask else out
         L = _lib.lib()
@@ -148,6 +153,7 @@ class CSRAdjacency:
             st = L.gc_spmm_csr_f32(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
                                    H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None, epi,
                                    out.data_ptr(), ldy, mask.data_ptr() if mask is not None else None,
+                                   gate.data_ptr() if gate is not None else None,
                                    plan.buf.data_ptr() if plan is not None else None,
                                    plan.n_pieces if plan is not None else 0, plan.n_cut if plan is not None else 0,
                                    scratch.data_ptr() if scratch is not None else None,
@@ -180,10 +186,10 @@ class DenseAdjacency:
         return self._symmetric
 
     def matmul(self, H: torch.Tensor, *, bias=None, relu=False, want_mask=False, accumulate_into=None, out=None,
-               precision=None):
+               precision=None, gate=None):
         from .ops import gemm
         _require(accumulate_into is None, "accumulate is not available on the dense path")
-        return gemm(self.A, H, bias=bias, relu=relu, want_mask=want_mask, precision=precision, out=out)
+        return gemm(self.A, H, bias=bias, relu=relu, want_mask=want_mask, precision=precision, out=out, gate=gate)
 
 
 # ---------------------------------------------------------------- conversion

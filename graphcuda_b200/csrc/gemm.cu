@@ -52,7 +52,7 @@ size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int
 
 int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float* C, int64_t ldc, const float* bias, int epilogue, float* mask,
-                int precision, void* workspace, size_t workspace_bytes, void* stream) {
+                const float* gate, int precision, void* workspace, size_t workspace_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gc_gemm_f32: negative size");
   GC_REQUIRE(M < INT32_MAX && N < INT32_MAX && K < INT32_MAX, "gc_gemm_f32: size out of int32 range");
   GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_TRANSPOSED_OUT)) == 0, "gc_gemm_f32: unknown epilogue bits");
@@ -64,7 +64,7 @@ int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K, const f
   GC_REQUIRE(lda >= (ta ? M : K), "gc_gemm_f32: lda too small");
   GC_REQUIRE(ldb >= (tb ? K : N), "gc_gemm_f32: ldb too small");
   GC_REQUIRE(ldc >= (tr ? M : N), "gc_gemm_f32: ldc too small");
-  gc::GemmEpilogue ep{bias, mask, (epilogue & GC_EPI_RELU) ? 1 : 0, tr ? 1 : 0};
+  gc::GemmEpilogue ep{bias, mask, gate, (epilogue & GC_EPI_RELU) ? 1 : 0, tr ? 1 : 0};
   cudaStream_t st = gc::as_stream(stream);
   int prec = (K == 0) ? GC_PREC_FP32_SIMT : resolve(ta, tb, M, N, K, lda, ldb, ldc, precision);
   if (prec < 0) return prec;

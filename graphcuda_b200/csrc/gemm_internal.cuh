@@ -10,6 +10,7 @@ namespace gc {
 struct GemmEpilogue {
   const float* bias;  // [N] or null
   float* mask;        // same shape / leading dimension as C, or null
+  const float* gate;  // same shape / leading dimension as C, or null: C *= (gate > 0) after everything else
   int relu;
   int transposed;     // store C^T (N x M, leading dimension ldc)
 };
@@ -23,6 +24,7 @@ __device__ __forceinline__ void epilogue_store(float v, int m, int n, float* C, 
     if (ep.mask) ep.mask[off] = mk;
     if (ep.relu) v *= mk;
   }
+  if (ep.gate) v *= (__ldg(ep.gate + off) > 0.f ? 1.f : 0.f);
   C[off] = v;
 }
 

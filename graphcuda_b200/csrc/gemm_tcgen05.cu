@@ -368,7 +368,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       float* Cb = raw_out ? p.partial + int64_t(split) * p.M * p.N : p.C;
       const int64_t ldc = raw_out ? int64_t(p.N) : p.ldc;
       gc::GemmEpilogue ep = p.ep;
-      if (raw_out) ep = gc::GemmEpilogue{nullptr, nullptr, 0, 0};
+      if (raw_out) ep = gc::GemmEpilogue{nullptr, nullptr, nullptr, 0, 0};
       const bool vec = raw_out ? (p.N % 4 == 0) : (p.vec_store != 0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -391,10 +391,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           // (pitch 33: conflict-free both ways) so that each store covers four
           // complete 128-byte row segments.
           float* tile = stage_tiles + (warp - 4) * (32 * 33);
+          const int c4 = (lane % 8) * 4;
+          // the gate values of all eight passes are requested before the block is turned, so their latency
+          // overlaps the shared-memory round trip (streaming loads: read once, keep them out of the caches)
+          float4 gv[8];
+          if (ep.gate) {
+#pragma unroll
+            for (int pass = 0; pass < 8; ++pass) {
+              const int gmr = m0 + q * 32 + pass * 4 + lane / 8;
+              gv[pass] = gmr < p.M ? __ldcs(reinterpret_cast<const float4*>(ep.gate + int64_t(gmr) * ldc + gn0 + c4))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(r[j]);
           __syncwarp();
-          const int c4 = (lane % 8) * 4;
 #pragma unroll
           for (int pass = 0; pass < 8; ++pass) {
             const int row = pass * 4 + lane / 8;
@@ -412,6 +423,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                                               v.w > 0.f ? 1.f : 0.f);
                 if (ep.mask) *reinterpret_cast<float4*>(ep.mask + int64_t(gmr) * ldc + gn0 + c4) = mk;
                 if (ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
+              }
+              if (ep.gate) {
+                v.x *= gv[pass].x > 0.f ? 1.f : 0.f; v.y *= gv[pass].y > 0.f ? 1.f : 0.f;
+                v.z *= gv[pass].z > 0.f ? 1.f : 0.f; v.w *= gv[pass].w > 0.f ? 1.f : 0.f;
               }
               *reinterpret_cast<float4*>(cptr) = v;
             }
@@ -728,7 +743,7 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
   p.ldc = ldc;
   p.ep = ep;
   p.flag = flag;
-  p.vec_store = (!ep.transposed && ldc % 4 == 0 && aligned16(C) && (!ep.mask || aligned16(ep.mask)) &&
+  p.vec_store = (!ep.transposed && ldc % 4 == 0 && aligned16(C) && (!ep.mask || aligned16(ep.mask)) && (!ep.gate || aligned16(ep.gate)) &&
                  (!ep.bias || aligned16(ep.bias)))
                     ? 1
                     : 0;

@@ -76,6 +76,7 @@ inline PlanView plan_view(void* plan, int64_t n_pieces, int64_t n_cut) {
 struct Epilogue {
   const float* bias;
   float* mask;
+  const float* gate;  // same shape / leading dimension as Y, or null: Y *= (gate > 0) after everything else
   int relu;
   int accumulate;
 };
@@ -88,6 +89,7 @@ struct Vec<4> {
   static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
   static __device__ __forceinline__ T load(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
   static __device__ __forceinline__ T load_plain(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ T load_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
   static __device__ __forceinline__ void store(float* p, T v) { *reinterpret_cast<float4*>(p) = v; }
   static __device__ __forceinline__ void fma(T& a, float s, const T& h) {
     a.x = fmaf(s, h.x, a.x);
@@ -111,6 +113,7 @@ struct Vec<1> {
   static __device__ __forceinline__ T zero() { return 0.f; }
   static __device__ __forceinline__ T load(const float* p) { return __ldg(p); }
   static __device__ __forceinline__ T load_plain(const float* p) { return *p; }
+  static __device__ __forceinline__ T load_stream(const float* p) { return __ldcs(p); }
   static __device__ __forceinline__ void store(float* p, T v) { *p = v; }
   static __device__ __forceinline__ void fma(T& a, float s, const T& h) { a = fmaf(s, h, a); }
   static __device__ __forceinline__ T add(const T& a, const T& b) { return a + b; }
@@ -121,7 +124,7 @@ struct Vec<1> {
 // Applies accumulate / bias / mask / ReLU to one vector and stores it.
 template <int VW>
 __device__ __forceinline__ void finish_store(typename Vec<VW>::T acc, float* yrow, float* mrow, int f,
-                                             const Epilogue& ep) {
+                                             const Epilogue& ep, const float* grow = nullptr) {
   using V = Vec<VW>;
   if (ep.accumulate) acc = V::add(acc, V::load_plain(yrow + f));
   if (ep.bias) acc = V::add(acc, V::load(ep.bias + f));
@@ -130,6 +133,7 @@ __device__ __forceinline__ void finish_store(typename Vec<VW>::T acc, float* yro
     if (mrow) V::store(mrow + f, m);
     if (ep.relu) acc = V::mul(acc, m);
   }
+  if (grow) acc = V::mul(acc, V::gt0(V::load_stream(grow + f)));  // read once: keep it out of the caches
   V::store(yrow + f, acc);
 }
 
@@ -139,8 +143,14 @@ __device__ __forceinline__ void finish_store(typename Vec<VW>::T acc, float* yro
 // PLANNED: pieces come from the plan (target >= 0: row of Y with the
 // epilogue; target < 0: scratch row ~target, raw sums); otherwise piece v is
 // row v of the matrix.
-template <int GROUP, int NACC, int VW, int U, bool PLANNED>
-__global__ void __launch_bounds__(256)
+// MIN_CTAS (resident CTAs per SM the register allocation must allow) is part
+// of the tuning: left to itself the compiler settles near 78 registers and
+// serialises the gathers; told its budget (80 registers at 3 CTAs, 128 at 2)
+// it keeps a whole round of U x NACC loads in flight.  Measured on the
+// 126 M-non-zero graph, F = 256: 12.6 ms unconstrained, 8.7 ms at 2, 8.4 ms
+// at 3; F = 100: 6.3 / 4.4 / 4.4 ms.
+template <int GROUP, int NACC, int VW, int U, bool PLANNED, int MIN_CTAS>
+__global__ void __launch_bounds__(256, MIN_CTAS)
 spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col,
                    const float* __restrict__ val, int n_pieces, const int32_t* __restrict__ p_start,
                    const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
@@ -169,8 +179,9 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
   if (!direct && (~target) >= slot_capacity) return;  // never write past the caller's scratch
   float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
   float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
+  const float* grow = (direct && ep.gate) ? ep.gate + int64_t(target) * ldY : nullptr;
   Epilogue my_ep = ep;
-  if (!direct) my_ep = Epilogue{nullptr, nullptr, 0, 0};
+  if (!direct) my_ep = Epilogue{nullptr, nullptr, nullptr, 0, 0};
 
   for (int f0 = 0; f0 < F; f0 += PASS) {
     typename V::T acc[NACC];
@@ -222,7 +233,7 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
     }
 #pragma unroll
     for (int a = 0; a < NACC; ++a)
-      if (live[a]) finish_store<VW>(acc[a], yrow, mrow, f0 + (a * GROUP + lane_g) * VW, my_ep);
+      if (live[a]) finish_store<VW>(acc[a], yrow, mrow, f0 + (a * GROUP + lane_g) * VW, my_ep, grow);
   }
 }
 
@@ -297,12 +308,13 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
   }
   float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
   float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
+  const float* grow = (direct && ep.gate) ? ep.gate + int64_t(target) * ldY : nullptr;
   Epilogue my_ep = ep;
-  if (!direct) my_ep = Epilogue{nullptr, nullptr, 0, 0};
+  if (!direct) my_ep = Epilogue{nullptr, nullptr, nullptr, 0, 0};
   // lane a stores vector a
 #pragma unroll
   for (int a = 0; a < NV; ++a)
-    if (lane_g == a && a < units) finish_store<4>(acc[a], yrow, mrow, a * 4, my_ep);
+    if (lane_g == a && a < units) finish_store<4>(acc[a], yrow, mrow, a * 4, my_ep, grow);
 }
 
 // One warp per cut row: adds that row's partial sums in slot order, then the
@@ -322,6 +334,7 @@ spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, cons
     const int s1 = min(s0 + __ldg(cut_nslots + i), slot_capacity);
     float* yrow = Y + int64_t(row) * ldY;
     float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
+    const float* grow = ep.gate ? ep.gate + int64_t(row) * ldY : nullptr;
     for (int f = lane * VW; f < F; f += 32 * VW) {
       typename V::T s = V::zero();
       int sl = s0;
@@ -332,7 +345,7 @@ spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, cons
         s = V::add(V::add(V::add(V::add(s, a), b), c), d);
       }
       for (; sl < s1; ++sl) s = V::add(s, V::load_plain(scratch + int64_t(sl) * ldS + f));
-      finish_store<VW>(s, yrow, mrow, f, ep);
+      finish_store<VW>(s, yrow, mrow, f, ep, grow);
     }
   }
 }
@@ -525,6 +538,12 @@ int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int pane
 }
 
 // ---------------------------------------------------------------- dispatch
+// Two resident CTAs (128 registers) for the 4-accumulator mappings on groups
+// of up to 8 lanes: on a 2.3 M-non-zero graph they run F = 48..128 in
+// 0.11-0.13 ms against 0.15-0.22 ms at three; everything else is as fast or
+// faster at three (F = 512 on 126 M non-zeros: 17.9 against 20.5 ms).
+constexpr int pieces_min_ctas(int group, int nacc, int vw) { return (vw == 4 && nacc == 4 && group <= 8) ? 2 : 3; }
+
 template <int GROUP, int NACC, int VW, int U>
 void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                    const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
@@ -532,12 +551,13 @@ void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, cons
                    cudaStream_t st) {
   constexpr int PER_CTA = 256 / GROUP;
   const unsigned grid = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
+  constexpr int MINB = pieces_min_ctas(GROUP, NACC, VW);
   if (planned)
-    spmm_pieces_kernel<GROUP, NACC, VW, U, true><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H,
-                                                                       ldH, Y, ldY, scratch, ldS, cap, ep);
+    spmm_pieces_kernel<GROUP, NACC, VW, U, true, MINB>
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ep);
   else
-    spmm_pieces_kernel<GROUP, NACC, VW, U, false><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F,
-                                                                        H, ldH, Y, ldY, scratch, ldS, cap, ep);
+    spmm_pieces_kernel<GROUP, NACC, VW, U, false, MINB>
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ep);
 }
 
 #define GC_PIECES(G, A, VWID, UU)                                                                                 \
@@ -702,8 +722,8 @@ size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F) {
 
 int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
                     const float* H, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
-                    float* mask, const void* plan, int64_t n_pieces, int64_t n_cut, void* scratch,
-                    size_t scratch_bytes, void* stream) {
+                    float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_cut,
+                    void* scratch, size_t scratch_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && F >= 0, "gc_spmm_csr_f32: negative size");
   GC_REQUIRE(M < INT32_MAX && K < INT32_MAX && F < INT32_MAX, "gc_spmm_csr_f32: size out of int32 range");
   GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_ACCUMULATE)) == 0, "gc_spmm_csr_f32: unknown epilogue bits");
@@ -712,10 +732,11 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
   GC_REQUIRE(ldY >= F && (K == 0 || ldH >= F), "gc_spmm_csr_f32: leading dimension smaller than F");
   GC_REQUIRE(K == 0 || H, "gc_spmm_csr_f32: null H");
   cudaStream_t st = gc::as_stream(stream);
-  Epilogue ep{bias, mask, (epilogue & GC_EPI_RELU) ? 1 : 0, (epilogue & GC_EPI_ACCUMULATE) ? 1 : 0};
+  Epilogue ep{bias, mask, gate, (epilogue & GC_EPI_RELU) ? 1 : 0, (epilogue & GC_EPI_ACCUMULATE) ? 1 : 0};
 
   const bool vec4 = (F % 4 == 0) && (ldH % 4 == 0) && (ldY % 4 == 0) && gc::aligned16(H) && gc::aligned16(Y) &&
-                    (!bias || gc::aligned16(bias)) && (!mask || gc::aligned16(mask));
+                    (!bias || gc::aligned16(bias)) && (!mask || gc::aligned16(mask)) &&
+                    (!gate || gc::aligned16(gate));
   const bool planned = plan != nullptr;
   const int32_t *ps = nullptr, *pl = nullptr, *pt = nullptr;
   PlanView pv{};
@@ -793,12 +814,12 @@ int static_scratch_for_current_device(float** out) {
 
 int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K,
                             int64_t F, const float* H, int64_t ldH, const float* bias, int epilogue, float* Y,
-                            int64_t ldY, float* mask, const void* plan, int64_t n_pieces, int64_t n_slots,
-                            int64_t n_cut, void* stream) {
+                            int64_t ldY, float* mask, const float* gate, const void* plan, int64_t n_pieces,
+                            int64_t n_slots, int64_t n_cut, void* stream) {
   GC_REQUIRE(n_slots >= 0, "gc_spmm_csr_f32_noalloc: negative n_slots");
   if (!plan || n_cut == 0)  // no cut rows, hence no scratch at all
-    return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, n_pieces, n_cut,
-                           nullptr, 0, stream);
+    return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, gate, plan, n_pieces,
+                           n_cut, nullptr, 0, stream);
   const size_t need = gc_spmm_scratch_bytes(n_slots, F);
   if (need > size_t(GC_SPMM_STATIC_SCRATCH_BYTES))
     return gc::fail(GC_ERR_WORKSPACE,
@@ -811,8 +832,8 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
   // Every partial-sum row the finalize pass reads is fully written by the
   // piece pass of the same call, so stale contents of the shared buffer are
   // never observed and nothing has to be cleared.
-  return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, plan, n_pieces, n_cut,
-                         scratch, size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
+  return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, gate, plan, n_pieces,
+                         n_cut, scratch, size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

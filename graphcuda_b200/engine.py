@@ -87,11 +87,20 @@ def layer_forward(X, adj, W, bias: Optional[torch.Tensor], relu: bool, *, want_m
 
 
 def layer_backward(dY, X, adj, W, relu: bool, Y, saved, *, need_dX: bool = True, need_dW: bool = True,
-                   need_db: bool = False, precision: Optional[str] = None):
+                   need_db: bool = False, precision: Optional[str] = None, grad_is_gated: bool = False,
+                   gate_dx_by_input: bool = False):
     """Gradients (dX, dW, db) of layer_forward; Y is the saved activation (the
-    ReLU mask is re-derived from it as Y > 0)."""
+    ReLU mask is re-derived from it as Y > 0).
+
+    Cross-layer fusion of the ReLU backward (reference gcn.cu:36): when this
+    layer's input X is itself the ReLU output of the layer below
+    (gate_dx_by_input), dX is multiplied by (X > 0) in the store of the kernel
+    that produces it -- which is exactly the masking the layer below would do
+    on its incoming gradient; that layer is then told its gradient arrives
+    gated (grad_is_gated) and skips the separate pass."""
     order, AX = saved
-    G = ops.relu_backward(dY, Y) if relu else dY
+    G = ops.relu_backward(dY, Y) if (relu and not grad_is_gated) else dY
+    gate = X if (gate_dx_by_input and need_dX and X.is_contiguous()) else None
     if G.stride(1) != 1:
         G = G.contiguous()
     dX = dW = db = None
@@ -106,21 +115,23 @@ def layer_backward(dY, X, adj, W, relu: bool, Y, saved, *, need_dX: bool = True,
         if need_dW:
             dW = ops.gemm(X.t(), S, precision=precision)[:, :out_dim]
         if need_dX:
-            dX = ops.gemm(S, Wp.t(), precision=precision)
+            dX = ops.gemm(S, Wp.t(), precision=precision, gate=gate)
         return dX, dW, db
     if order == "aggregate_first":
         if need_dW:
             dW = ops.gemm(AX.t(), G, precision=precision)
         if need_dX:
             T = ops.gemm(G, W.t(), precision=precision)
-            dX = _adj_matmul(adj, T, precision)  # A, not A^T: reference gcn.cu:49
+            dX = _adj_matmul(adj, T, precision, gate=gate)  # A, not A^T: reference gcn.cu:49
     else:
         # Y = A (X W), A symmetric: S = A^T G = A G
         S = _adj_matmul(adj, G, precision)
         if need_dW:
             dW = ops.gemm(X.t(), S, precision=precision)
         if need_dX:
-            dX = ops.gemm(S, W.t(), precision=precision)
+            dX = ops.gemm(S, W.t(), precision=precision, gate=gate)
+    if gate_dx_by_input and need_dX and gate is None:  # non-contiguous input: separate pass
+        dX = ops.relu_backward(dX, X)
     return dX, dW, db
 
 

@@ -29,7 +29,9 @@ class GCNConvFunction(torch.autograd.Function):
     aggregated features are saved instead of being recomputed (gcn.cu:40)."""
 
     @staticmethod
-    def forward(ctx, X, adjm, weights, apply_relu, bias=None, precision=None):
+    def forward(ctx, X, adjm, weights, apply_relu, bias=None, precision=None, fuse=0):
+        # fuse: bit 0 = the incoming gradient is already multiplied by this layer's ReLU mask;
+        #       bit 1 = X is the ReLU output of the layer below: gate dX by (X > 0) where it is produced
         adj = as_adjacency(adjm)
         Y, _, saved = layer_forward(X, adj, weights, bias, bool(apply_relu), precision=precision)
         order, inter = saved
@@ -39,6 +41,7 @@ class GCNConvFunction(torch.autograd.Function):
         ctx.precision = precision
         ctx.has_bias = bias is not None
         ctx.has_inter = inter is not None
+        ctx.fuse = int(fuse)
         tensors = [X, weights, Y]
         if inter is not None:
             tensors.append(inter)
@@ -54,8 +57,9 @@ class GCNConvFunction(torch.autograd.Function):
         need_db = ctx.has_bias and ctx.needs_input_grad[4]
         dX, dW, db = layer_backward(grad_Y.contiguous(), X, ctx.adj, weights, ctx.apply_relu, Y,
                                     (ctx.order, inter), need_dX=need_dX, need_dW=need_dW, need_db=need_db,
-                                    precision=ctx.precision)
-        return dX, None, dW, None, db, None
+                                    precision=ctx.precision, grad_is_gated=bool(ctx.fuse & 1),
+                                    gate_dx_by_input=bool(ctx.fuse & 2))
+        return dX, None, dW, None, db, None, None
 
 
 class GCNConv(nn.Module):
@@ -66,6 +70,9 @@ class GCNConv(nn.Module):
         self.out_dim = out_dim
         self.apply_relu = apply_relu
         self.precision = precision
+        # Set by a container that knows the layer's neighbours (models.GCN): see GCNConvFunction.forward.
+        # Only valid when this layer's output feeds exactly one consumer that gates its input gradient.
+        self.fuse_relu_backward = 0
 
         stdv = math.sqrt(2.0 / (in_dim + out_dim))
         self.weights = Parameter(torch.Tensor(in_dim, out_dim))
@@ -76,4 +83,5 @@ class GCNConv(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, X: torch.Tensor, adjm) -> torch.Tensor:
-        return GCNConvFunction.apply(X, adjm, self.weights, self.apply_relu, self.bias, self.precision)
+        return GCNConvFunction.apply(X, adjm, self.weights, self.apply_relu, self.bias, self.precision,
+                                     self.fuse_relu_backward)

@@ -11,11 +11,18 @@ from .gcn import GCNConv
 
 
 class GCN(torch.nn.Module):
-    def __init__(self, dims: Sequence[int], *, precision: Optional[str] = None):
+    def __init__(self, dims: Sequence[int], *, precision: Optional[str] = None, fuse_relu_backward: bool = True):
         super().__init__()
         self.convs = torch.nn.ModuleList(
             [GCNConv(dims[i], dims[i + 1], apply_relu=(i < len(dims) - 2), precision=precision)
              for i in range(len(dims) - 1)])
+        if fuse_relu_backward:
+            # Layer i's ReLU output has exactly one consumer here (layer i + 1), so the ReLU backward of layer i
+            # is applied where layer i + 1 produces its input gradient (reference gcn.cu:36 as a fused store).
+            for lower, upper in zip(self.convs[:-1], self.convs[1:]):
+                if lower.apply_relu:
+                    lower.fuse_relu_backward |= 1
+                    upper.fuse_relu_backward |= 2
 
     def forward(self, x, adj, log_softmax: bool = True):
         """log_softmax=False returns the last layer's raw output, for

@@ -116,10 +116,11 @@ def _as_operand(t: torch.Tensor):
 # ---------------------------------------------------------------- GEMM
 def gemm(A: torch.Tensor, B: torch.Tensor, *, bias: Optional[torch.Tensor] = None, relu: bool = False,
          want_mask: bool = False, precision: Optional[str] = None, transposed_out: bool = False,
-         out: Optional[torch.Tensor] = None):
+         out: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
     """C = A @ B (+bias)(ReLU) in fp32.  A and B may be transposed views.
     Returns C, or (C, mask) when want_mask.  With transposed_out the result
-    tensor holds C^T (shape N x M)."""
+    tensor holds C^T (shape N x M).  gate (contiguous, shape of the result):
+    the result is multiplied by (gate > 0) in the store."""
     _require(A.dim() == 2 and B.dim() == 2, "Inputs must be 2D")
     _require(A.size(1) == B.size(0), "A.cols must match B.rows")
     _require(A.is_cuda and B.is_cuda, "Inputs must be CUDA tensors")
@@ -141,6 +142,10 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         if bias is not None:
             _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == N, "bias must be float32 [N]")
             bias = bias.contiguous()
+        if gate is not None:
+            _require(gate.is_cuda and gate.dtype == torch.float32 and tuple(gate.shape) == shape
+                     and gate.is_contiguous() and out.is_contiguous(), "gate must be a contiguous float32 tensor "
+                     "of the result's shape")
         if M and N:
             L = _lib.lib()
             prec = _prec(precision)
@@ -150,7 +155,8 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
             st = L.gc_gemm_f32(ta, tb, M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(),
                                max(out.stride(0), 1) if out.size(0) > 1 else max(out.size(1), 1),
                                bias.data_ptr() if bias is not None else None, epi,
-                               mask.data_ptr() if mask is not None else None, prec, ws.data_ptr(), ws.numel(),
+                               mask.data_ptr() if mask is not None else None,
+                               gate.data_ptr() if gate is not None else None, prec, ws.data_ptr(), ws.numel(),
                                _stream(dev))
             _lib.check(st, "gc_gemm_f32")
     return (out, mask) if want_mask else out

@@ -97,13 +97,17 @@ size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F);
  * (the fp32 mask of reference gcn.cu:19).  plan may be null: then every row is
  * one piece in natural order (n_pieces, n_cut ignored, no scratch needed).
  * With a plan, n_pieces and n_cut are the counts it was built with.
+ * gate, when non-null, is a matrix of Y's shape and leading dimension: the
+ * result is multiplied by (gate > 0) last of all -- the ReLU mask of the
+ * PREVIOUS layer (reference gcn.cu:36) applied where this layer's input
+ * gradient is produced, instead of in a separate pass.
  * No atomics: results are deterministic run to run.
  */
 int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
                     int64_t M, int64_t K, int64_t F,
                     const float* H, int64_t ldH,
                     const float* bias, int epilogue,
-                    float* Y, int64_t ldY, float* mask,
+                    float* Y, int64_t ldY, float* mask, const float* gate,
                     const void* plan, int64_t n_pieces, int64_t n_cut,
                     void* scratch, size_t scratch_bytes,
                     void* stream);
@@ -139,7 +143,7 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
                             int64_t M, int64_t K, int64_t F,
                             const float* H, int64_t ldH,
                             const float* bias, int epilogue,
-                            float* Y, int64_t ldY, float* mask,
+                            float* Y, int64_t ldY, float* mask, const float* gate,
                             const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
                             void* stream);
 
@@ -153,8 +157,8 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
  * (gemm_cublas.cu:11-16 called from gcn.cu:43,46): op(A)/op(B) are read in
  * place.
  *
- * C[M,N] = op(A)[M,K] * op(B)[K,N] (+ bias[N]) (ReLU), optional fp32 mask as
- * above (leading dimension ldc).  transA=0: A is stored M x K; transA=1: A is
+ * C[M,N] = op(A)[M,K] * op(B)[K,N] (+ bias[N]) (ReLU), optional fp32 mask and
+ * optional gate input as above (leading dimension ldc).  transA=0: A is stored M x K; transA=1: A is
  * stored K x M.  transB likewise (transB=0: K x N; transB=1: N x K).
  */
 #define GC_PREC_AUTO (-1)      /* fp32 semantics: TF32X3 on tensor cores when the shape qualifies, else FP32_SIMT */
@@ -168,7 +172,7 @@ size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int
 int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K,
                 const float* A, int64_t lda, const float* B, int64_t ldb,
                 float* C, int64_t ldc,
-                const float* bias, int epilogue, float* mask,
+                const float* bias, int epilogue, float* mask, const float* gate,
                 int precision, void* workspace, size_t workspace_bytes,
                 void* stream);
 /* Which path gc_gemm_f32 would take for these arguments: one of GC_PREC_*

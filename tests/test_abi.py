@@ -43,7 +43,7 @@ def test_header_cites_the_reference():
 
 def test_status_strings_and_version():
     L = _lib.lib()
-    assert L.gc_abi_version() >= 1
+    assert L.gc_abi_version() >= 2
     assert L.gc_status_string(0) == b"ok"
     assert b"workspace" in L.gc_status_string(-4)
 
@@ -51,15 +51,15 @@ def test_status_strings_and_version():
 def test_argument_validation_without_gpu():
     L = _lib.lib()
     # negative size
-    assert L.gc_gemm_f32(0, 0, -1, 4, 4, None, 4, None, 4, None, 4, None, 0, None, 0, None, 0, None) == -1
+    assert L.gc_gemm_f32(0, 0, -1, 4, 4, None, 4, None, 4, None, 4, None, 0, None, None, 0, None, 0, None) == -1
     assert b"negative" in L.gc_last_error()
     # leading dimension too small
-    assert L.gc_gemm_f32(0, 0, 8, 8, 8, 16, 4, 16, 8, 16, 8, None, 0, None, 0, None, 0, None) == -1
+    assert L.gc_gemm_f32(0, 0, 8, 8, 8, 16, 4, 16, 8, 16, 8, None, 0, None, None, 0, None, 0, None) == -1
     # unknown epilogue bit
-    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, 0, 0, None, 0, None) == -1
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, None, 0, 0, None, 0, None) == -1
     # empty problems succeed without launching anything
-    assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, 0, None, 0, None) == 0
-    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, 0, 0, None, 0, None) == 0
+    assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, None, 0, None, 0, None) == 0
+    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, 0, None, 0, None) == 0
     with pytest.raises(RuntimeError):
         _lib.check(-1, "probe")
 

@@ -320,3 +320,38 @@ def test_cuda_graph_replay_matches_eager_training(cuda):
     assert torch.equal(lg, loss)
     for a, b in zip(m1.parameters(), m2.parameters()):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dims", [[24, 32, 40, 7], [64, 32, 16, 7], [100, 256, 256, 47]])
+def test_fused_relu_backward_equals_separate_pass(cuda, dims):
+    """models.GCN applies a layer's ReLU backward in the store of the kernel that
+    produces the upper layer's input gradient (SpMM or GEMM).  Multiplying by the
+    same 0/1 mask in another place changes no bit of any gradient."""
+    import graphcuda_b200 as gc
+    from graphcuda_b200 import synth
+    from graphcuda_b200.models import GCN
+    n = 6000 if dims[1] < 256 else 20000
+    A = _graph(n, 12, seed=3)
+    adj = gc.as_adjacency(A.to(cuda), symmetric=True)
+    X = synth.normal_features(n, dims[0], seed=4, device=cuda)
+    y = synth.uniform_labels(n, dims[-1], seed=5, device=cuda)
+    grads = []
+    for fuse in (True, False):
+        torch.manual_seed(1)
+        m = GCN(dims, fuse_relu_backward=fuse).to(cuda)
+        assert [c.fuse_relu_backward for c in m.convs] == ([1, 3, 2] if fuse else [0, 0, 0])
+        Xg = X.clone().requires_grad_()
+        loss = gc.log_softmax_nll_loss(m(Xg, adj, log_softmax=False), y)
+        loss.backward()
+        grads.append([Xg.grad.clone()] + [c.weights.grad.clone() for c in m.convs])
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
+    # and against the oracle model (ties excluded by the tolerance: two ReLUs, rare mask flips)
+    torch.manual_seed(1)
+    ref = O.GCN(dims)
+    Xr = X.cpu().clone().requires_grad_()
+    lr = torch.nn.functional.nll_loss(ref(Xr, A), y.cpu())
+    lr.backward()
+    assert O.rel_fro(grads[0][0], Xr.grad) < 2e-3
+    for gw, conv in zip(grads[0][1:], ref.convs):
+        assert O.rel_fro(gw, conv.weights.grad) < 2e-3

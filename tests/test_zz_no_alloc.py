@@ -24,7 +24,7 @@ def _call_noalloc(L, adj, H, Y, bias=None, epilogue=0, n_slots=None):
     plan = adj.plan_for(F)
     return L.gc_spmm_csr_f32_noalloc(
         adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), M, K, F,
-        H.data_ptr(), F, bias.data_ptr() if bias is not None else None, epilogue, Y.data_ptr(), F, None,
+        H.data_ptr(), F, bias.data_ptr() if bias is not None else None, epilogue, Y.data_ptr(), F, None, None,
         plan.buf.data_ptr(), plan.n_pieces, plan.n_slots if n_slots is None else n_slots, plan.n_cut,
         torch.cuda.current_stream().cuda_stream)
 
