@@ -415,7 +415,7 @@ def run_ours(args):
         # dram__bytes_read.sum + dram__bytes_write.sum of the F = 256 launch (pieces + finalize kernels), captured
         # with ncu on the half-size graph and scaled by the non-zeros (profiles/spmm_pieces_kernel_rmat_products.md);
         # the compulsory bytes of that launch are 6.04e9
-        "traffic": 21.8e9 if (args.shrink == 1 and world == 1) else None,
+        "traffic": 21.7e9 if (args.shrink == 1 and world == 1) else None,
         "traffic_note": "bytes per F=256 launch at full size on 1 GPU; compulsory 6.04e9",
     }
 

@@ -538,11 +538,11 @@ int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int pane
 }
 
 // ---------------------------------------------------------------- dispatch
-// Two resident CTAs (128 registers) for the 4-accumulator mappings on groups
+// Two resident CTAs (128 registers) for the 3- and 4-accumulator mappings on groups
 // of up to 8 lanes: on a 2.3 M-non-zero graph they run F = 48..128 in
 // 0.11-0.13 ms against 0.15-0.22 ms at three; everything else is as fast or
 // faster at three (F = 512 on 126 M non-zeros: 17.9 against 20.5 ms).
-constexpr int pieces_min_ctas(int group, int nacc, int vw) { return (vw == 4 && nacc == 4 && group <= 8) ? 2 : 3; }
+constexpr int pieces_min_ctas(int group, int nacc, int vw) { return (vw == 4 && nacc >= 3 && group <= 8) ? 2 : 3; }
 
 template <int GROUP, int NACC, int VW, int U>
 void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
@@ -593,6 +593,7 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
   }
   if (units <= 4) GC_PIECES(4, 1, 4, 4);
   else if (units <= 8) GC_PIECES(8, 1, 4, 8);
+  else if (units <= 12) GC_PIECES(4, 3, 4, 4);  // F = 48 on 126 M non-zeros: 2.24 ms against 2.35 ms with a fourth, idle vector
   else if (units <= 16) GC_PIECES(4, 4, 4, 4);
   else if (units <= 32) GC_PIECES(8, 4, 4, 4);
   else if (units <= 64) GC_PIECES(16, 4, 4, 4);
