@@ -21,7 +21,8 @@ from .adjacency import (CSRAdjacency, DenseAdjacency, as_adjacency, gcn_norm,  #
                         normalized_adjacency)
 from .gcn import GCNConv, GCNConvFunction  # noqa: E402
 from .graphed import GraphedTrainStep  # noqa: E402
-from .losses import log_softmax_nll_loss  # noqa: E402
+from .losses import argmax_accuracy, log_softmax_nll_loss  # noqa: E402
+from .optim import FusedAdam, FusedSGD  # noqa: E402
 from .ops import gemm, get_default_precision, set_default_precision  # noqa: E402
 
 cpp_ext = _graphcuda

@@ -50,6 +50,10 @@ SIGNATURES = {
                                              _void]),
     "gc_logsoftmax_nll_backward_f32": (_int, [_f32p, _i64, _i64p, _void, _i64, _i64, C.c_float, _f32p, _f32p, _i64,
                                               _void, _void]),
+    "gc_argmax_accuracy_f32": (_int, [_f32p, _i64, _i64, _i64, _i64p, _void, _int, _i64p, _i64p, _void]),
+    "gc_adam_step_f32": (_int, [_int, _void, _void, _void, _void, _void, C.c_double, C.c_double, C.c_double,
+                                C.c_double, C.c_double, _void, _void]),
+    "gc_sgd_step_f32": (_int, [_int, _void, _void, _void, C.c_double, C.c_double, _void]),
     "gc_coo_rows_to_rowptr": (_int, [_i64p, _i64, _i64, _i32p, _void]),
     "gc_narrow_i64_i32": (_int, [_i64p, _i32p, _i64, _void]),
     "gc_gcn_norm_f32": (_int, [_i64p, _i64p, _i64, _i64, _f32p, _f32p, _void]),

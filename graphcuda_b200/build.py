@@ -31,7 +31,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "elementwise.cu",
     "graph_build.cu",
-    "loss.cu",
+    "loss.cu", "optim.cu",
 ]
 
 NVCC_FLAGS = [

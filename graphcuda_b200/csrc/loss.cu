@@ -100,6 +100,73 @@ lse_nll_backward_kernel(const float* __restrict__ Z, int64_t ldz, const int64_t*
   }
 }
 
+// Evaluation tail (reference tests/gcn/graphcuda_impl.py:63-68): row-wise
+// argmax (lowest index among equal maxima) and, for each of n_masks row
+// selections, how many selected rows were predicted right and how many were
+// selected.  Integer atomics: the counts do not depend on the order.
+__global__ void __launch_bounds__(256)
+argmax_count_kernel(const float* __restrict__ Z, int64_t ldz, int64_t M, int C, const int64_t* __restrict__ labels,
+                    const uint8_t* __restrict__ masks, int n_masks, int64_t* __restrict__ pred,
+                    unsigned long long* __restrict__ counts) {
+  __shared__ unsigned int sh[8][2 * 8];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int64_t warps = int64_t(gridDim.x) * 8;
+  unsigned int right[8], chosen[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) right[m] = chosen[m] = 0;
+  for (int64_t r = int64_t(blockIdx.x) * 8 + warp; r < M; r += warps) {
+    const float* z = Z + r * ldz;
+    float best = -INFINITY;
+    int arg = C;  // no finite or infinite candidate seen yet
+    for (int c = lane; c < C; c += 32) {
+      const float v = __ldg(z + c);
+      if (v > best || arg == C) {
+        best = v;
+        arg = c;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (oa < C && (arg == C || ob > best || (ob == best && oa < arg))) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if (lane == 0) {
+      if (pred) pred[r] = arg;
+      if (labels) {
+        const bool hit = labels[r] == int64_t(arg);
+        if (masks) {
+          for (int m = 0; m < n_masks; ++m)
+            if (masks[int64_t(m) * M + r]) {
+              chosen[m]++;
+              right[m] += hit ? 1u : 0u;
+            }
+        } else {
+          chosen[0]++;
+          right[0] += hit ? 1u : 0u;
+        }
+      }
+    }
+  }
+  if (!labels) return;
+  const int nm = masks ? n_masks : 1;
+  if (lane == 0)
+    for (int m = 0; m < nm; ++m) {
+      sh[warp][2 * m] = right[m];
+      sh[warp][2 * m + 1] = chosen[m];
+    }
+  __syncthreads();
+  if (threadIdx.x < 2 * nm) {
+    unsigned long long t = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sh[w][threadIdx.x];
+    if (t) atomicAdd(counts + threadIdx.x, t);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -139,6 +206,27 @@ int gc_logsoftmax_nll_backward_f32(const float* Z, int64_t ldz, const int64_t* l
   lse_nll_backward_kernel<<<blocks, 256, 0, gc::as_stream(stream)>>>(Z, ldz, labels, row_mask, lse, grad_loss, scale,
                                                                     M, int(C), dZ, lddz);
   return gc::check_launch("gc_logsoftmax_nll_backward_f32");
+}
+
+int gc_argmax_accuracy_f32(const float* Z, int64_t ldz, int64_t M, int64_t C, const int64_t* labels,
+                           const uint8_t* masks, int n_masks, int64_t* pred, int64_t* counts, void* stream) {
+  GC_REQUIRE(M >= 0 && C >= 1 && C < INT32_MAX, "gc_argmax_accuracy_f32: bad size");
+  GC_REQUIRE(ldz >= C, "gc_argmax_accuracy_f32: leading dimension smaller than C");
+  GC_REQUIRE(n_masks >= 0 && n_masks <= 8, "gc_argmax_accuracy_f32: at most 8 row selections");
+  GC_REQUIRE(!masks || n_masks >= 1, "gc_argmax_accuracy_f32: masks given with n_masks = 0");
+  GC_REQUIRE(!labels || counts, "gc_argmax_accuracy_f32: labels given without counts");
+  GC_REQUIRE(M == 0 || Z, "gc_argmax_accuracy_f32: null Z");
+  cudaStream_t st = gc::as_stream(stream);
+  if (labels) {
+    const int nm = masks ? n_masks : 1;
+    if (cudaMemsetAsync(counts, 0, size_t(2 * nm) * sizeof(int64_t), st) != cudaSuccess)
+      return gc::fail(GC_ERR_CUDA, "gc_argmax_accuracy_f32: clearing the counts failed");
+  }
+  if (M == 0 || (!pred && !labels)) return GC_OK;
+  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + 7) / 8, kLossBlocks)));
+  argmax_count_kernel<<<blocks, 256, 0, st>>>(Z, ldz, M, int(C), labels, masks, n_masks, pred,
+                                              reinterpret_cast<unsigned long long*>(counts));
+  return gc::check_launch("gc_argmax_accuracy_f32");
 }
 
 }  // extern "C"

@@ -23,8 +23,13 @@ class GraphedTrainStep:
     """step() = zero_grad; loss = log_softmax_nll(model(X, adj)[, mask]); backward; optimizer.step().
 
     X, labels and mask are static buffers: refresh them in place
-    (``step.X.copy_(new_X)``) between replays.  The optimizer must be
-    capturable (e.g. ``torch.optim.Adam(..., capturable=True)``)."""
+    (``step.X.copy_(new_X)``) between replays.
+    Build it before the model is trained eagerly on another stream: autograd
+    ties a parameter's gradient accumulation to the stream of its first use for
+    as long as that step's graph is referenced, and a launch on the default
+    stream is illegal during capture.  The optimizer must be
+    capturable: ``graphcuda_b200.FusedAdam`` (one launch, step count on the
+    device) or e.g. ``torch.optim.Adam(..., capturable=True)``."""
 
     def __init__(self, model, adj, X: torch.Tensor, labels: torch.Tensor, optimizer,
                  row_mask: Optional[torch.Tensor] = None, warmup: int = 3):
@@ -35,7 +40,7 @@ class GraphedTrainStep:
         side.wait_stream(torch.cuda.current_stream(X.device))
         with torch.cuda.stream(side):
             for _ in range(max(warmup, 1)):
-                self._eager_step()
+                self.warmup_loss = self._eager_step()  # loss of the last eager step, for callers that log it
         torch.cuda.current_stream(X.device).wait_stream(side)
         torch.cuda.synchronize(X.device)
         self.graph = torch.cuda.CUDAGraph()

@@ -68,3 +68,47 @@ def log_softmax_nll_loss(logits: torch.Tensor, labels: torch.Tensor, row_mask: O
         cnt = int(row_mask.sum().item()) if row_mask is not None else logits.size(0)
         scale = 1.0 / max(cnt, 1)
     return _LogSoftmaxNLL.apply(logits, labels, row_mask, scale)
+
+
+def argmax_accuracy(logits: torch.Tensor, labels: Optional[torch.Tensor] = None, masks=None, *,
+                    want_pred: bool = True):
+    """The evaluation tail of the reference's script (tests/gcn/graphcuda_impl.py:63-68) in one kernel.
+
+    Returns ``(pred, counts)``: ``pred`` = ``logits.argmax(dim=1)`` (int64; lowest index among equal
+    maxima; None when want_pred is False), ``counts`` = int64 tensor ``[n, 2]`` on the device with, per
+    row selection, the number of selected rows predicted right and the number selected (None without
+    labels).  ``masks``: None (all rows), one bool / uint8 vector, or a sequence of up to 8 of them.
+    Nothing is read back to the host: ``counts[:, 0] / counts[:, 1]`` are the accuracies."""
+    if not (logits.is_cuda and logits.dim() == 2 and logits.dtype == torch.float32):
+        raise RuntimeError("argmax_accuracy: float32 CUDA matrix expected")
+    Z = logits if logits.stride(1) == 1 or logits.size(1) == 1 else logits.contiguous()
+    M, C = Z.shape
+    dev = Z.device
+    mask_mat = None
+    n_masks = 0
+    if masks is not None:
+        if labels is None:
+            raise RuntimeError("argmax_accuracy: masks need labels")
+        rows = [masks] if isinstance(masks, torch.Tensor) and masks.dim() == 1 else list(masks)
+        if not 1 <= len(rows) <= 8:
+            raise RuntimeError("argmax_accuracy: between 1 and 8 row selections")
+        for m in rows:
+            if m.numel() != M or m.device != dev:
+                raise RuntimeError("argmax_accuracy: every selection needs one entry per row, on the logits' device")
+        mask_mat = torch.stack([m.reshape(M).ne(0) for m in rows]).to(torch.uint8).contiguous()
+        n_masks = len(rows)
+    if labels is not None:
+        if not (labels.dtype == torch.int64 and labels.numel() == M and labels.device == dev):
+            raise RuntimeError("argmax_accuracy: labels must be int64 [M] on the logits' device")
+        labels = labels.contiguous()
+    with torch.cuda.device(dev):
+        pred = torch.empty(M, dtype=torch.int64, device=dev) if want_pred else None
+        counts = torch.empty((max(n_masks, 1), 2), dtype=torch.int64, device=dev) if labels is not None else None
+        st = _lib.lib().gc_argmax_accuracy_f32(
+            Z.data_ptr(), Z.stride(0) if M > 1 else max(C, 1), M, C,
+            labels.data_ptr() if labels is not None else None,
+            mask_mat.data_ptr() if mask_mat is not None else None, n_masks,
+            pred.data_ptr() if pred is not None else None,
+            counts.data_ptr() if counts is not None else None, _stream(dev))
+        _lib.check(st, "gc_argmax_accuracy_f32")
+    return pred, counts

@@ -8,6 +8,7 @@ from typing import Optional, Sequence
 import torch
 
 from .gcn import GCNConv
+from .losses import argmax_accuracy
 
 
 class GCN(torch.nn.Module):
@@ -30,3 +31,12 @@ class GCN(torch.nn.Module):
         for conv in self.convs:
             x = conv(x, adj)
         return torch.log_softmax(x, dim=1) if log_softmax else x
+
+    @torch.no_grad()
+    def evaluate(self, x, adj, labels, masks=None):
+        """The reference script's ``test()`` (tests/gcn/graphcuda_impl.py:60-69): a forward pass without
+        autograd state (nothing is saved, no mask is written, log_softmax is skipped because it does not
+        move the argmax) followed by the fused argmax / count kernel.  Returns ``(pred, counts)`` as
+        losses.argmax_accuracy does; ``(counts[:, 0] / counts[:, 1]).tolist()`` gives the accuracies with
+        one host read."""
+        return argmax_accuracy(self.forward(x, adj, log_softmax=False), labels, masks)

@@ -217,6 +217,44 @@ int gc_logsoftmax_nll_backward_f32(const float* Z, int64_t ldz, const int64_t* l
                                    int64_t M, int64_t C, float scale, const float* grad_loss,
                                    float* dZ, int64_t lddz, const void* workspace, void* stream);
 
+/*
+ * Evaluation tail of the reference's script (tests/gcn/graphcuda_impl.py:63-68:
+ * out.argmax(dim=1), then (pred[mask] == y[mask]).sum() / mask.sum() for the
+ * train / validation / test selections) in one pass over Z.
+ * pred (int64[M], may be null): index of the row maximum, the lowest index
+ * among equal maxima (argmax of log_softmax(Z) and of Z coincide, so the
+ * logits can be passed as they are).
+ * With labels: counts[2 m] = selected rows of selection m predicted right,
+ * counts[2 m + 1] = rows selection m holds; masks is n_masks x M bytes
+ * (row-major, non-zero = selected), n_masks <= 8; masks null = one selection
+ * of all rows.  counts (int64[2 * max(n_masks, 1)]) is cleared by the call.
+ */
+int gc_argmax_accuracy_f32(const float* Z, int64_t ldz, int64_t M, int64_t C, const int64_t* labels,
+                           const uint8_t* masks, int n_masks, int64_t* pred, int64_t* counts, void* stream);
+
+/* ---- optimizer step (reference tests/gcn/graphcuda_impl.py:45,56) --------- */
+
+/*
+ * The optimizer.step() of the reference's training script for every parameter
+ * tensor in one launch.  params / grads / exp_avg / exp_avg_sq and sizes are
+ * HOST arrays of n_tensors (<= 32) device pointers / element counts, read
+ * during the call; all tensors contiguous fp32.
+ * gc_adam_step_f32: torch.optim.Adam's update (amsgrad and maximize off,
+ * weight_decay added to the gradient; hyper-parameters are doubles as in
+ * Python, 1 - beta and the bias corrections are formed in double and rounded
+ * once).  `state` is 16 bytes of device memory,
+ * zero before the first step: the step count (uint64) lives there and is
+ * advanced by the kernel, so a recorded launch can be replayed.
+ * gc_sgd_step_f32: p -= lr * (g + weight_decay * p), the SGD the reference's
+ * script constructs (no momentum).
+ */
+int gc_adam_step_f32(int n_tensors, float* const* params, const float* const* grads,
+                     float* const* exp_avg, float* const* exp_avg_sq, const int64_t* sizes,
+                     double lr, double beta1, double beta2, double eps, double weight_decay,
+                     void* state, void* stream);
+int gc_sgd_step_f32(int n_tensors, float* const* params, const float* const* grads, const int64_t* sizes,
+                    double lr, double weight_decay, void* stream);
+
 /* ---- adjacency construction (reference tests/gcn/graphcuda_impl.py:27-38) - */
 
 /*

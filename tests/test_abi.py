@@ -60,6 +60,14 @@ def test_argument_validation_without_gpu():
     # empty problems succeed without launching anything
     assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, None, 0, None, 0, None) == 0
     assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, 0, None, 0, None) == 0
+    # evaluation tail and optimizer step: bad arguments are refused before any launch
+    assert L.gc_argmax_accuracy_f32(16, 2, 4, 3, None, None, 0, None, None, None) == -1  # ld < C
+    assert L.gc_argmax_accuracy_f32(16, 4, 4, 3, None, 16, 9, None, None, None) == -1  # more than 8 selections
+    assert L.gc_argmax_accuracy_f32(None, 4, 0, 3, None, None, 0, None, None, None) == 0  # no rows
+    assert L.gc_adam_step_f32(33, 16, 16, 16, 16, 16, 0.01, 0.9, 0.999, 1e-8, 0.0, 16, None) == -1
+    assert b"tensors" in L.gc_last_error()
+    assert L.gc_adam_step_f32(1, 16, 16, 16, 16, 16, 0.01, 0.9, 0.999, 1e-8, 0.0, None, None) == -1  # null state
+    assert L.gc_sgd_step_f32(0, None, None, None, 0.1, 0.0, None) == 0
     with pytest.raises(RuntimeError):
         _lib.check(-1, "probe")
 

@@ -355,3 +355,38 @@ def test_fused_relu_backward_equals_separate_pass(cuda, dims):
     assert O.rel_fro(grads[0][0], Xr.grad) < 2e-3
     for gw, conv in zip(grads[0][1:], ref.convs):
         assert O.rel_fro(gw, conv.weights.grad) < 2e-3
+
+
+def test_evaluate_matches_the_scripts_test_function(cuda):
+    """GCN.evaluate = the reference script's test() (tests/gcn/graphcuda_impl.py:60-69): no-grad forward,
+    argmax, per-split accuracy; compared with the oracle model carrying the same weights."""
+    from graphcuda_b200 import synth
+    from graphcuda_b200.models import GCN
+    cfg = synth.CONFIGS["cora_like"]
+    n = cfg["nodes"]
+    e = synth.preferential_attachment_edges(n, cfg["edges"], cfg["seed"])
+    A = O.normalized_adjacency_coo(synth.symmetrize(e), n)
+    X = synth.bow_features(n, cfg["features"], 0.0127, seed=1)
+    y = synth.uniform_labels(n, cfg["classes"], seed=2)
+    splits = synth.planetoid_split(n)
+    dims = [cfg["features"], cfg["hidden"], cfg["classes"]]
+    torch.manual_seed(3)
+    ref = O.GCN(dims)
+    torch.manual_seed(3)
+    model = GCN(dims).to(cuda)
+    with torch.no_grad():
+        out = ref(X, A)
+    pr = out.argmax(1)
+    want = [[int(((pr == y) & m).sum()), int(m.sum())] for m in splits]
+    pred, counts = model.evaluate(X.to(cuda), A.to(cuda), y.to(cuda), [m.to(cuda) for m in splits])
+    got = counts.cpu().tolist()
+    flips = int((pred.cpu() != pr).sum())
+    if flips == 0:
+        assert got == want
+    else:  # only numerical ties may flip
+        bad = (pred.cpu() != pr).nonzero().flatten()
+        top2 = out[bad].double().topk(2, dim=1).values
+        assert float((top2[:, 0] - top2[:, 1]).max()) < 1e-6
+    assert [c[1] for c in got] == [140, 500, 1000]
+    # no autograd state is kept by the evaluation pass
+    assert all(p.grad is None for p in model.parameters())
