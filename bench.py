@@ -53,7 +53,7 @@ def parse():
     ap.add_argument("--cpu-sample-div", type=int, default=32)
     ap.add_argument("--partition", default="auto", choices=["auto", "features", "rows"],
                     help="multi-GPU scheme: aggregation sharded over feature columns (all-to-all) or adjacency rows "
-                         "(all-gather); auto = rows at 2 GPUs, features from 4 (measured cross-over)")
+                         "(all-gather); auto = rows up to 4 GPUs, features from 8 (measured cross-over)")
     ap.add_argument("--profile-warmup", action="store_true",
                     help="honour --warmup below 3 (profiler captures only; such a run is not a benchmark)")
     return ap.parse_args()
@@ -269,7 +269,7 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.partition == "auto":
-        args.partition = "features" if world >= 4 else "rows"
+        args.partition = "features" if world >= 8 else "rows"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local)
