@@ -374,24 +374,34 @@ def run_ours(args):
     # ---- end to end: pinned host inputs copied in, loss read back, every step ----
     Xh = X.cpu().pin_memory()
     yh = y.cpu().pin_memory()
-    Xd = torch.empty_like(X)
-    yd = torch.empty_like(y)
+    feed = gc.PinnedFeed(dev, like=[X, y])
 
-    def e2e_step():
-        Xd.copy_(Xh, non_blocking=True)
-        yd.copy_(yh, non_blocking=True)
-        Xg = part.prepare_constant(Xd) if world > 1 else None
-        return float(step(Xd, yd, Xg).item())  # .item() is the device-to-host read of the result
+    def e2e_run(k: int, overlap: bool) -> None:
+        """k steps, each with its own host->device copy of the inputs and a device->host read of the loss.
+        overlap: the copy of step i + 1 is issued before step i computes (input prefetch, as a data loader does);
+        otherwise copy and compute alternate.  The first copy is never hidden."""
+        feed.submit([Xh, yh])
+        for i in range(k):
+            Xd, yd = feed.take()
+            if overlap and i + 1 < k:
+                feed.submit([Xh, yh])
+            Xg = part.prepare_constant(Xd) if world > 1 else None
+            loss = step(Xd, yd, Xg)
+            feed.release()
+            float(loss.item())  # the device-to-host read of the result
+            if not overlap and i + 1 < k:
+                feed.submit([Xh, yh])
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    e2e_times = {}
+    for overlap in (False, True):
+        e2e_run(2, overlap)
+        barrier()
+        e0.record()
+        e2e_run(args.steps, overlap)
+        e1.record()
+        barrier()
+        e2e_times[overlap] = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    e2e_ms = e2e_times[True]
     h2d = Xh.numel() * 4 + yh.numel() * 8
     if world > 1:
         t = torch.tensor([h2d], dtype=torch.float64, device=dev)
@@ -424,7 +434,11 @@ def run_ours(args):
         "warmup": n_warm, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(cfg, args, world),
         "roofline": roofline,
-        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * world},
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * world,
+                "how": "public API (GCN + log_softmax_nll_loss + FusedAdam) fed by PinnedFeed: every step copies its "
+                       "features and labels from pinned host memory and reads the loss back; the copy of step i+1 is "
+                       "in flight while step i computes, the first copy of the timed region is exposed",
+                "value_without_prefetch": e2e_times[False]},
         "gpu_launches": int(launches), "clocks": clocks, "final_loss": final_loss, "setup_s": setup_s,
         "spmm_gbs": achieved, "spmm_pct_hbm_peak": 100.0 * achieved / peak,
     }

@@ -20,6 +20,7 @@ from ._graphcuda import (gemm_cublas, matmul1, matmul2, matmul3, matmul4,  # noq
 from .adjacency import (CSRAdjacency, DenseAdjacency, as_adjacency, gcn_norm,  # noqa: E402
                         normalized_adjacency)
 from .gcn import GCNConv, GCNConvFunction  # noqa: E402
+from .feed import PinnedFeed  # noqa: E402
 from .graphed import GraphedTrainStep  # noqa: E402
 from .losses import argmax_accuracy, log_softmax_nll_loss  # noqa: E402
 from .optim import FusedAdam, FusedSGD  # noqa: E402
