@@ -573,8 +573,9 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
                    cudaStream_t st) {
   const int units = F / 4;  // 128-bit vectors per row
   // Measured on the 126 M-non-zero graph: up to 8 floats the lane-per-non-zero kernel wins (F = 8: 0.99 ms
-  // against 2.0 ms); from 12 to 32 floats one 128-bit vector per lane with 4-8 non-zeros in flight per lane
-  // does (F = 32: 1.74 ms against 3.4 ms for 2 lanes x 4 vectors and 4.2 ms for lane-per-non-zero).
+  // against 2.0 ms); from 12 to 32 floats groups of 4 lanes with one or two 128-bit vectors per lane and 4
+  // non-zeros in flight do (F = 32: 1.5 ms against 1.7 ms for 8 lanes x 1 vector, 3.4 ms for 2 lanes x 4
+  // vectors and 4.2 ms for lane-per-non-zero).
   if (units <= 2) {
     const unsigned grid = unsigned((n_pieces + 31) / 32);
 #define GC_NARROW(NV, UU)                                                                                       \
@@ -592,7 +593,7 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
     return;
   }
   if (units <= 4) GC_PIECES(4, 1, 4, 4);
-  else if (units <= 8) GC_PIECES(8, 1, 4, 8);
+  else if (units <= 8) GC_PIECES(4, 2, 4, 4);  // F = 32: 1.54 ms; 8 lanes x 1 vector x 8 in flight: 1.73 ms
   else if (units <= 12) GC_PIECES(4, 3, 4, 4);  // F = 48 on 126 M non-zeros: 2.24 ms against 2.35 ms with a fourth, idle vector
   else if (units <= 16) GC_PIECES(4, 4, 4, 4);
   else if (units <= 32) GC_PIECES(8, 4, 4, 4);
