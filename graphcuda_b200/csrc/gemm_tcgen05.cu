@@ -40,7 +40,7 @@ constexpr int BM = 128;
 template <int BN, int PASSES>
 constexpr int block_k() { return (PASSES == 3 && BN == 256) ? 16 : 32; }
 constexpr int UMMA_K = 8;   // K of one kind::tf32 instruction
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;  // 16 warps: producer, MMA issuer, TMEM allocator, idle | 4 epilogue | 4 converter | 4 epilogue
 constexpr uint32_t kWaitLimit = 1u << 24;
 
 // ------------------------------------------------------------------ PTX
@@ -183,7 +183,7 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kStageBytes = (PASSES == 3 ? 2 : 1) * (kABytes + kBBytes);
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  static constexpr int kStagingBytes = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 tile per epilogue warp
+  static constexpr int kStagingBytes = 8 * 32 * 32 * 4;  // one 32 x 32 fp32 tile per epilogue warp
   static constexpr int kSmemBytes =
       kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStagingBytes;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -249,7 +249,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull(b), 1);
-      mbar_init(bar_tempty(b), 4);
+      mbar_init(bar_tempty(b), 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -349,9 +349,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if (ok) umma_commit(bar_tfull(b));
       }
     }
-  } else if (warp >= 4 && warp < 8) {
+  } else if ((warp >= 4 && warp < 8) || warp >= 12) {
     // ------------------------------------------------------------ epilogue
-    const int q = warp - 4;  // TMEM lane quarter == warp id % 4
+    // Two warps per TMEM lane quarter (a warp may only read lanes 32 * (warp % 4) ...): group 0 takes the even
+    // 32-column chunks of a tile, group 1 the odd ones.  A single warp per scheduler left the epilogue bound by
+    // the latency of its own dependent instructions (about 0.8 us per chunk whatever the chunk did).
+    const int q = warp % 4;             // TMEM lane quarter
+    const int grp = warp >= 12 ? 1 : 0;  // chunk parity
     uint32_t tcount = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++tcount) {
@@ -370,13 +374,32 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       gc::GemmEpilogue ep = p.ep;
       if (raw_out) ep = gc::GemmEpilogue{nullptr, nullptr, nullptr, 0, 0};
       const bool vec = raw_out ? (p.N % 4 == 0) : (p.vec_store != 0);
+      // Gate values of the NEXT tile of this CTA are requested into the L2 now, a whole tile time before the
+      // epilogue reads them (they come from DRAM: 128 KB per tile, read once).
+      if (ep.gate && item + int(gridDim.x) < num_items) {
+        int nm0, nn0, nk0, nk1, nsplit;
+        item_coords(item + int(gridDim.x), nm0, nn0, nk0, nk1, nsplit);
+        const int prow = nm0 + q * 32 + lane;
+        if (prow < p.M) {
+          const char* g = reinterpret_cast<const char*>(ep.gate + int64_t(prow) * ldc + nn0);
+          const int bytes = min(BN, p.N - nn0) * 4;
+          for (int off = grp * 128; off < bytes; off += 256) asm volatile("prefetch.global.L2 [%0];" ::"l"(g + off));
+        }
+      }
+      // Row r of the 32 x 32 block a warp stores in one pass: lanes 8k..8k+7 cover the 128 bytes of row 4*pass + k.
+      const int c4 = (lane % 8) * 4;
+      const int row_in_quarter = lane / 8;
+      const int64_t row0_off = int64_t(m0 + q * 32 + row_in_quarter) * ldc + c4;  // element offset of pass 0
+      const int rows_left = p.M - (m0 + q * 32 + row_in_quarter);                // pass valid iff 4 * pass < rows_left
+      float4* tile4 = reinterpret_cast<float4*>(stage_tiles + (grp * 4 + q) * (32 * 32));
+      uint32_t r[32];
+      tmem_ld32(taddr + uint32_t(grp * 32), r);
+      tmem_ld_wait();
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + uint32_t(c * 32), r);
-        tmem_ld_wait();
+      for (int c = grp; c < BN / 32; c += 2) {
         const int gn0 = n0 + c * 32;
-        if (gn0 >= p.N) continue;  // uniform across the warp
+        if (gn0 >= p.N) break;  // uniform across the warp; nothing is in flight here
+        const bool have_next = c + 2 < BN / 32;
         if (ep.transposed) {
           // lanes hold consecutive m: a column of C is a contiguous run of C^T
 #pragma unroll
@@ -384,61 +407,62 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             const int gn = gn0 + j;
             if (gn < p.N && gm < p.M) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
           }
+          if (have_next) tmem_ld32(taddr + uint32_t((c + 2) * 32), r);
         } else if (vec && gn0 + 32 <= p.N) {
-          // The accumulator arrives one row per lane.  Stored like that, every
-          // 128-bit store of the warp would touch 32 different lines (half a
-          // sector each).  The 32 x 32 block is turned through shared memory
-          // (pitch 33: conflict-free both ways) so that each store covers four
-          // complete 128-byte row segments.
-          float* tile = stage_tiles + (warp - 4) * (32 * 33);
-          const int c4 = (lane % 8) * 4;
-          // the gate values of all eight passes are requested before the block is turned, so their latency
-          // overlaps the shared-memory round trip (streaming loads: read once, keep them out of the caches)
+          // The accumulator arrives one row per lane.  Stored like that, every 128-bit store of the warp would
+          // touch 32 different lines.  The 32 x 32 block is turned through shared memory -- 128-bit accesses both
+          // ways, the 16-byte chunk index XORed with the row so that neither direction has bank conflicts -- and
+          // every store instruction covers four complete 128-byte row segments.  The TMEM load of the next 32
+          // columns and the gate values of this block are in flight while the block is turned.
           float4 gv[8];
           if (ep.gate) {
 #pragma unroll
-            for (int pass = 0; pass < 8; ++pass) {
-              const int gmr = m0 + q * 32 + pass * 4 + lane / 8;
-              gv[pass] = gmr < p.M ? __ldcs(reinterpret_cast<const float4*>(ep.gate + int64_t(gmr) * ldc + gn0 + c4))
-                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+            for (int pass = 0; pass < 8; ++pass)
+              gv[pass] = 4 * pass < rows_left
+                             ? __ldcs(reinterpret_cast<const float4*>(ep.gate + row0_off + int64_t(4 * pass) * ldc + gn0))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
           }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(r[j]);
+          for (int j4 = 0; j4 < 8; ++j4)
+            tile4[lane * 8 + (j4 ^ (lane & 7))] =
+                make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]),
+                            __uint_as_float(r[4 * j4 + 3]));
+          if (have_next) tmem_ld32(taddr + uint32_t((c + 2) * 32), r);
           __syncwarp();
+          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (ep.bias) bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + c4));
 #pragma unroll
           for (int pass = 0; pass < 8; ++pass) {
-            const int row = pass * 4 + lane / 8;
-            const int gmr = m0 + q * 32 + row;
-            const float* tp = tile + row * 33 + c4;
-            float4 v = make_float4(tp[0], tp[1], tp[2], tp[3]);
-            if (gmr < p.M) {
-              float* cptr = Cb + int64_t(gmr) * ldc + gn0 + c4;
-              if (ep.bias) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + c4));
-                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-              }
+            const int row = pass * 4 + row_in_quarter;
+            float4 v = tile4[row * 8 + ((lane & 7) ^ (row & 7))];
+            if (4 * pass < rows_left) {
+              const int64_t off = row0_off + int64_t(4 * pass) * ldc + gn0;
+              v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
               if (ep.relu || ep.mask) {
                 const float4 mk = make_float4(v.x > 0.f ? 1.f : 0.f, v.y > 0.f ? 1.f : 0.f, v.z > 0.f ? 1.f : 0.f,
                                               v.w > 0.f ? 1.f : 0.f);
-                if (ep.mask) *reinterpret_cast<float4*>(ep.mask + int64_t(gmr) * ldc + gn0 + c4) = mk;
+                if (ep.mask) *reinterpret_cast<float4*>(ep.mask + off) = mk;
                 if (ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
               }
               if (ep.gate) {
                 v.x *= gv[pass].x > 0.f ? 1.f : 0.f; v.y *= gv[pass].y > 0.f ? 1.f : 0.f;
                 v.z *= gv[pass].z > 0.f ? 1.f : 0.f; v.w *= gv[pass].w > 0.f ? 1.f : 0.f;
               }
-              *reinterpret_cast<float4*>(cptr) = v;
+              *reinterpret_cast<float4*>(Cb + off) = v;
             }
           }
           __syncwarp();
-        } else if (gm < p.M) {
+        } else {
+          if (gm < p.M) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int gn = gn0 + j;
-            if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
+            for (int j = 0; j < 32; ++j) {
+              const int gn = gn0 + j;
+              if (gn < p.N) gc::epilogue_store(__uint_as_float(r[j]), gm, gn, Cb, ldc, ep);
+            }
           }
+          if (have_next) tmem_ld32(taddr + uint32_t((c + 2) * 32), r);
         }
+        if (have_next) tmem_ld_wait();
       }
       tc_fence_before();
       __syncwarp();
