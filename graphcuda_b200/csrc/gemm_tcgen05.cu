@@ -431,47 +431,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           __syncwarp();
           float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
           if (ep.bias) bv = __ldg(reinterpret_cast<const float4*>(ep.bias + gn0 + c4));
-          // Four row segments at a time are handled phase by phase (load, bias, ReLU / mask, gate, store) so that
-          // four independent chains overlap; pass by pass the warp would wait out every latency on its own, and
-          // eight at a time do not fit the 128 registers a 512-thread CTA leaves each thread.
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float4 v[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int row = (half * 4 + i) * 4 + row_in_quarter;
-              v[i] = tile4[row * 8 + ((lane & 7) ^ (row & 7))];
-            }
-            if (ep.bias) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                v[i].x += bv.x; v[i].y += bv.y; v[i].z += bv.z; v[i].w += bv.w;
+          for (int pass = 0; pass < 8; ++pass) {
+            const int row = pass * 4 + row_in_quarter;
+            float4 v = tile4[row * 8 + ((lane & 7) ^ (row & 7))];
+            if (4 * pass < rows_left) {
+              const int64_t off = row0_off + int64_t(4 * pass) * ldc + gn0;
+              v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              if (ep.relu || ep.mask) {
+                const float4 mk = make_float4(v.x > 0.f ? 1.f : 0.f, v.y > 0.f ? 1.f : 0.f, v.z > 0.f ? 1.f : 0.f,
+                                              v.w > 0.f ? 1.f : 0.f);
+                if (ep.mask) *reinterpret_cast<float4*>(ep.mask + off) = mk;
+                if (ep.relu) { v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w; }
               }
-            }
-            if (ep.relu || ep.mask) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int pass = half * 4 + i;
-                const float4 mk = make_float4(v[i].x > 0.f ? 1.f : 0.f, v[i].y > 0.f ? 1.f : 0.f,
-                                              v[i].z > 0.f ? 1.f : 0.f, v[i].w > 0.f ? 1.f : 0.f);
-                if (ep.mask && 4 * pass < rows_left)
-                  *reinterpret_cast<float4*>(ep.mask + row0_off + int64_t(4 * pass) * ldc + gn0) = mk;
-                if (ep.relu) { v[i].x *= mk.x; v[i].y *= mk.y; v[i].z *= mk.z; v[i].w *= mk.w; }
+              if (ep.gate) {
+                v.x *= gv[pass].x > 0.f ? 1.f : 0.f; v.y *= gv[pass].y > 0.f ? 1.f : 0.f;
+                v.z *= gv[pass].z > 0.f ? 1.f : 0.f; v.w *= gv[pass].w > 0.f ? 1.f : 0.f;
               }
-            }
-            if (ep.gate) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int pass = half * 4 + i;
-                v[i].x *= gv[pass].x > 0.f ? 1.f : 0.f; v[i].y *= gv[pass].y > 0.f ? 1.f : 0.f;
-                v[i].z *= gv[pass].z > 0.f ? 1.f : 0.f; v[i].w *= gv[pass].w > 0.f ? 1.f : 0.f;
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int pass = half * 4 + i;
-              if (4 * pass < rows_left)
-                *reinterpret_cast<float4*>(Cb + row0_off + int64_t(4 * pass) * ldc + gn0) = v[i];
+              *reinterpret_cast<float4*>(Cb + off) = v;
             }
           }
           __syncwarp();
