@@ -8,8 +8,8 @@
 //   loss = scale * sum over selected rows r of ( logsumexp(Z[r, :]) - Z[r, y_r] )
 //   dZ[r, c] = g * scale * ( exp(Z[r, c] - lse_r) - [c == y_r] )   for selected rows, 0 otherwise
 //
-// One warp per row, lanes across classes (coalesced), shuffles for the max /
-// sum; the loss is reduced per warp, per block and by a final single block in
+// A group of lanes per row (8 lanes up to 64 classes, else the warp), lanes across classes, shuffles for the
+// max / sum; the loss is reduced per warp, per block and by a final single block in
 // a fixed order (no atomics, bit-reproducible).
 #include "common.cuh"
 
@@ -19,35 +19,35 @@ namespace {
 
 constexpr int kLossBlocks = gc::kNumSMs * 8;
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-
+// G lanes per row (8 for up to 64 classes, else the whole warp): 32 / G rows are in flight per warp, so the
+// per-row chain of two reductions and a logf is overlapped within the warp as well as across warps.
+template <int G>
 __global__ void __launch_bounds__(256)
 lse_nll_forward_kernel(const float* __restrict__ Z, int64_t ldz, const int64_t* __restrict__ labels,
                        const uint8_t* __restrict__ row_mask, int64_t M, int C, float* __restrict__ lse,
                        float* __restrict__ partials) {
   __shared__ float warp_loss[8];
+  constexpr int R = 32 / G;  // rows per warp pass
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-  const int64_t warps = int64_t(gridDim.x) * 8;
+  const int lg = lane % G, sub = lane / G;
+  const int64_t stride = int64_t(gridDim.x) * 8 * R;
   float acc = 0.f;
-  for (int64_t r = int64_t(blockIdx.x) * 8 + warp; r < M; r += warps) {
-    const float* z = Z + r * ldz;
+  for (int64_t r0 = (int64_t(blockIdx.x) * 8 + warp) * R; r0 < M; r0 += stride) {  // uniform across the warp
+    const int64_t r = r0 + sub;
+    const bool valid = r < M;
+    const float* z = Z + (valid ? r : 0) * ldz;
     float mx = -INFINITY;
-    for (int c = lane; c < C; c += 32) mx = fmaxf(mx, __ldg(z + c));
-    mx = warp_max(mx);
+    if (valid)
+      for (int c = lg; c < C; c += G) mx = fmaxf(mx, __ldg(z + c));
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float s = 0.f;
-    for (int c = lane; c < C; c += 32) s += expf(__ldg(z + c) - mx);
-    s = warp_sum(s);
-    const float l = mx + logf(s);
-    if (lane == 0) {
+    if (valid)
+      for (int c = lg; c < C; c += G) s += expf(__ldg(z + c) - mx);
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (valid && lg == 0) {
+      const float l = mx + logf(s);
       lse[r] = l;
       if (!row_mask || row_mask[r]) {
         const int64_t y = labels[r];
@@ -55,6 +55,9 @@ lse_nll_forward_kernel(const float* __restrict__ Z, int64_t ldz, const int64_t* 
       }
     }
   }
+  // the R row-slots of the warp, then the 8 warps, in a fixed order
+#pragma unroll
+  for (int o = 16; o >= G; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) warp_loss[warp] = acc;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -79,24 +82,27 @@ loss_reduce_kernel(const float* __restrict__ partials, int n, float scale, float
   if (threadIdx.x == 0) *loss = sh[0] * scale;
 }
 
+template <int G>
 __global__ void __launch_bounds__(256)
 lse_nll_backward_kernel(const float* __restrict__ Z, int64_t ldz, const int64_t* __restrict__ labels,
                         const uint8_t* __restrict__ row_mask, const float* __restrict__ lse,
                         const float* __restrict__ grad_loss, float scale, int64_t M, int C, float* __restrict__ dZ,
                         int64_t lddz) {
+  constexpr int R = 32 / G;
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-  const int64_t warps = int64_t(gridDim.x) * 8;
+  const int lg = lane % G, sub = lane / G;
+  const int64_t stride = int64_t(gridDim.x) * 8 * R;
   const float g = (grad_loss ? __ldg(grad_loss) : 1.f) * scale;
-  for (int64_t r = int64_t(blockIdx.x) * 8 + warp; r < M; r += warps) {
+  for (int64_t r = (int64_t(blockIdx.x) * 8 + warp) * R + sub; r < M; r += stride) {
     float* d = dZ + r * lddz;
     if (row_mask && !row_mask[r]) {
-      for (int c = lane; c < C; c += 32) d[c] = 0.f;
+      for (int c = lg; c < C; c += G) d[c] = 0.f;
       continue;
     }
     const float* z = Z + r * ldz;
     const float l = __ldg(lse + r);
     const int64_t y = labels[r];
-    for (int c = lane; c < C; c += 32) d[c] = g * (expf(__ldg(z + c) - l) - (c == y ? 1.f : 0.f));
+    for (int c = lg; c < C; c += G) d[c] = g * (expf(__ldg(z + c) - l) - (c == y ? 1.f : 0.f));
   }
 }
 
@@ -188,8 +194,12 @@ int gc_logsoftmax_nll_forward_f32(const float* Z, int64_t ldz, const int64_t* la
   cudaStream_t st = gc::as_stream(stream);
   float* partials = static_cast<float*>(workspace);
   float* lse = partials + kLossBlocks;
-  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + 7) / 8, kLossBlocks)));
-  lse_nll_forward_kernel<<<blocks, 256, 0, st>>>(Z, ldz, labels, row_mask, M, int(C), lse, partials);
+  const int rows_per_block = C <= 64 ? 32 : 8;
+  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + rows_per_block - 1) / rows_per_block, kLossBlocks)));
+  if (C <= 64)
+    lse_nll_forward_kernel<8><<<blocks, 256, 0, st>>>(Z, ldz, labels, row_mask, M, int(C), lse, partials);
+  else
+    lse_nll_forward_kernel<32><<<blocks, 256, 0, st>>>(Z, ldz, labels, row_mask, M, int(C), lse, partials);
   loss_reduce_kernel<<<1, 256, 0, st>>>(partials, blocks, scale, loss);
   return gc::check_launch("gc_logsoftmax_nll_forward_f32", 2);
 }
@@ -202,9 +212,14 @@ int gc_logsoftmax_nll_backward_f32(const float* Z, int64_t ldz, const int64_t* l
   GC_REQUIRE(Z && labels && dZ && workspace, "gc_logsoftmax_nll_backward_f32: null pointer");
   GC_REQUIRE(ldz >= C && lddz >= C, "gc_logsoftmax_nll_backward_f32: leading dimension smaller than C");
   const float* lse = static_cast<const float*>(workspace) + kLossBlocks;
-  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + 7) / 8, kLossBlocks)));
-  lse_nll_backward_kernel<<<blocks, 256, 0, gc::as_stream(stream)>>>(Z, ldz, labels, row_mask, lse, grad_loss, scale,
-                                                                    M, int(C), dZ, lddz);
+  const int rows_per_block = C <= 64 ? 32 : 8;
+  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + rows_per_block - 1) / rows_per_block, kLossBlocks)));
+  if (C <= 64)
+    lse_nll_backward_kernel<8><<<blocks, 256, 0, gc::as_stream(stream)>>>(Z, ldz, labels, row_mask, lse, grad_loss,
+                                                                         scale, M, int(C), dZ, lddz);
+  else
+    lse_nll_backward_kernel<32><<<blocks, 256, 0, gc::as_stream(stream)>>>(Z, ldz, labels, row_mask, lse, grad_loss,
+                                                                          scale, M, int(C), dZ, lddz);
   return gc::check_launch("gc_logsoftmax_nll_backward_f32");
 }
 
