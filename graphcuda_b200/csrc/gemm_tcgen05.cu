@@ -632,9 +632,10 @@ Plan make_plan(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int passes) {
     pl.transpose_a = true;
   }
   // Pre-splitting B (weights) costs a second tile load per stage; making B_lo in shared memory costs converter
-  // time.  Measured on 2.4 M-row operands: in-kernel wins while the tile's MMA work is small (K * BN < 256 * 256:
-  // 1.35 -> 1.12 ms at K = 100, N = 256) and loses slightly at K = N = 256 (1.61 -> 1.68 ms).
-  pl.conv_b = pl.b_mn || !(small_b) || (K * pl.bn < 256 * 256);
+  // time.  In-kernel wins while the tile's MMA work is small.  Measured on 1.2 M-row operands, in shared memory
+  // against pre-split: K x BN = 100 x 256 0.48 / 0.63 ms, 128 x 256 0.50 / 0.48 ms, 256 x 128 0.58 / 0.48 ms,
+  // 256 x 256 0.80 / 0.81 ms, 256 x 64 and 48 x 256 equal.
+  pl.conv_b = pl.b_mn || !(small_b) || (K * pl.bn < 128 * 256);
   if (passes != 3) pl.conv_b = pl.b_mn;  // selects the template only
   const int64_t tiles = gc::ceil_div(M, BM) * gc::ceil_div(N, pl.bn);
   const int bk = (passes == 3 && pl.bn == 256) ? 16 : 32;
