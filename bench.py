@@ -446,6 +446,9 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_aux:
         try:
             line["aux"] = aux_measurements(dev, args)
+            # the script's test(): no-grad forward of the same model + fused argmax / accuracy counts
+            line["aux"]["rmat_products_eval_forward_argmax_ms"] = _time_ms(lambda: model.evaluate(X, adj, y), warm=2,
+                                                                          iters=5)
         except Exception as ex:  # auxiliary numbers never take the headline down
             line["aux"] = {"error": repr(ex)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

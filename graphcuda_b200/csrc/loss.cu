@@ -110,29 +110,35 @@ lse_nll_backward_kernel(const float* __restrict__ Z, int64_t ldz, const int64_t*
 // argmax (lowest index among equal maxima) and, for each of n_masks row
 // selections, how many selected rows were predicted right and how many were
 // selected.  Integer atomics: the counts do not depend on the order.
+template <int G>
 __global__ void __launch_bounds__(256)
 argmax_count_kernel(const float* __restrict__ Z, int64_t ldz, int64_t M, int C, const int64_t* __restrict__ labels,
                     const uint8_t* __restrict__ masks, int n_masks, int64_t* __restrict__ pred,
                     unsigned long long* __restrict__ counts) {
   __shared__ unsigned int sh[8][2 * 8];
+  constexpr int R = 32 / G;  // rows per warp pass, G lanes each
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-  const int64_t warps = int64_t(gridDim.x) * 8;
+  const int lg = lane % G, sub = lane / G;
+  const int64_t stride = int64_t(gridDim.x) * 8 * R;
   unsigned int right[8], chosen[8];
 #pragma unroll
   for (int m = 0; m < 8; ++m) right[m] = chosen[m] = 0;
-  for (int64_t r = int64_t(blockIdx.x) * 8 + warp; r < M; r += warps) {
-    const float* z = Z + r * ldz;
+  for (int64_t r0 = (int64_t(blockIdx.x) * 8 + warp) * R; r0 < M; r0 += stride) {  // uniform across the warp
+    const int64_t r = r0 + sub;
+    const bool valid = r < M;
+    const float* z = Z + (valid ? r : 0) * ldz;
     float best = -INFINITY;
-    int arg = C;  // no finite or infinite candidate seen yet
-    for (int c = lane; c < C; c += 32) {
-      const float v = __ldg(z + c);
-      if (v > best || arg == C) {
-        best = v;
-        arg = c;
+    int arg = C;  // no candidate seen yet
+    if (valid)
+      for (int c = lg; c < C; c += G) {
+        const float v = __ldg(z + c);
+        if (v > best || arg == C) {
+          best = v;
+          arg = c;
+        }
       }
-    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = G / 2; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
       const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
       if (oa < C && (arg == C || ob > best || (ob == best && oa < arg))) {
@@ -140,13 +146,14 @@ argmax_count_kernel(const float* __restrict__ Z, int64_t ldz, int64_t M, int C, 
         arg = oa;
       }
     }
-    if (lane == 0) {
+    if (valid && lg == 0) {
       if (pred) pred[r] = arg;
       if (labels) {
         const bool hit = labels[r] == int64_t(arg);
         if (masks) {
-          for (int m = 0; m < n_masks; ++m)
-            if (masks[int64_t(m) * M + r]) {
+#pragma unroll
+          for (int m = 0; m < 8; ++m)  // fixed trip count: the counters stay in registers
+            if (m < n_masks && masks[int64_t(m) * M + r]) {
               chosen[m]++;
               right[m] += hit ? 1u : 0u;
             }
@@ -159,11 +166,21 @@ argmax_count_kernel(const float* __restrict__ Z, int64_t ldz, int64_t M, int C, 
   }
   if (!labels) return;
   const int nm = masks ? n_masks : 1;
-  if (lane == 0)
-    for (int m = 0; m < nm; ++m) {
-      sh[warp][2 * m] = right[m];
-      sh[warp][2 * m + 1] = chosen[m];
+  // the R row-slots of a warp (their leaders are lanes 0, G, 2G, ...), then the 8 warps
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    if (m < nm) {  // uniform
+#pragma unroll
+      for (int o = 16; o >= G; o >>= 1) {
+        right[m] += __shfl_xor_sync(0xffffffffu, right[m], o);
+        chosen[m] += __shfl_xor_sync(0xffffffffu, chosen[m], o);
+      }
+      if (lane == 0) {
+        sh[warp][2 * m] = right[m];
+        sh[warp][2 * m + 1] = chosen[m];
+      }
     }
+  }
   __syncthreads();
   if (threadIdx.x < 2 * nm) {
     unsigned long long t = 0;
@@ -238,9 +255,14 @@ int gc_argmax_accuracy_f32(const float* Z, int64_t ldz, int64_t M, int64_t C, co
       return gc::fail(GC_ERR_CUDA, "gc_argmax_accuracy_f32: clearing the counts failed");
   }
   if (M == 0 || (!pred && !labels)) return GC_OK;
-  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + 7) / 8, kLossBlocks)));
-  argmax_count_kernel<<<blocks, 256, 0, st>>>(Z, ldz, M, int(C), labels, masks, n_masks, pred,
-                                              reinterpret_cast<unsigned long long*>(counts));
+  const int rows_per_block = C <= 64 ? 32 : 8;
+  const int blocks = int(std::max<int64_t>(1, std::min<int64_t>((M + rows_per_block - 1) / rows_per_block, kLossBlocks)));
+  if (C <= 64)
+    argmax_count_kernel<8><<<blocks, 256, 0, st>>>(Z, ldz, M, int(C), labels, masks, n_masks, pred,
+                                                   reinterpret_cast<unsigned long long*>(counts));
+  else
+    argmax_count_kernel<32><<<blocks, 256, 0, st>>>(Z, ldz, M, int(C), labels, masks, n_masks, pred,
+                                                    reinterpret_cast<unsigned long long*>(counts));
   return gc::check_launch("gc_argmax_accuracy_f32");
 }
 
