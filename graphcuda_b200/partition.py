@@ -87,9 +87,9 @@ class CudaBackend:
     def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
         return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into, out=out)
 
-    def gemm(self, A, B, *, bias=None, relu=False, precision=None):
+    def gemm(self, A, B, *, bias=None, relu=False, precision=None, gate=None):
         from . import ops
-        return ops.gemm(A, B, bias=bias, relu=relu, precision=precision)
+        return ops.gemm(A, B, bias=bias, relu=relu, precision=precision, gate=gate)
 
     def relu_backward(self, dY, Y):
         from . import ops
@@ -297,7 +297,9 @@ class DistGCNConvFunction(torch.autograd.Function):
     The returned weight gradient is already summed over ranks."""
 
     @staticmethod
-    def forward(ctx, X, graph, W, apply_relu, bias, precision, X_gathered):
+    def forward(ctx, X, graph, W, apply_relu, bias, precision, X_gathered, fuse=0):
+        # fuse: bit 0 = the incoming gradient is already multiplied by this layer's ReLU mask;
+        #       bit 1 = X is the ReLU output of the layer below: hand dX over multiplied by (X > 0)
         be = graph.backend
         fin, fout = W.shape
         transform_first = fout < fin  # the partitioned adjacency is symmetric by contract
@@ -322,6 +324,7 @@ class DistGCNConvFunction(torch.autograd.Function):
         ctx.precision = precision
         ctx.has_bias = bias is not None
         ctx.has_inter = inter is not None
+        ctx.fuse = int(fuse)
         ctx.save_for_backward(*([X, W, Y] + ([inter] if inter is not None else [])))
         return Y
 
@@ -334,7 +337,8 @@ class DistGCNConvFunction(torch.autograd.Function):
         need_dX = ctx.needs_input_grad[0]
         need_dW = ctx.needs_input_grad[2]
         dY = dY.contiguous()
-        G = be.relu_backward(dY, Y) if ctx.apply_relu else dY
+        G = be.relu_backward(dY, Y) if (ctx.apply_relu and not ctx.fuse & 1) else dY
+        gate_dx = bool(ctx.fuse & 2)
         dX = dW = db = None
         if ctx.has_bias and ctx.needs_input_grad[4]:
             db = graph.all_reduce_sum(G.sum(0))
@@ -344,8 +348,8 @@ class DistGCNConvFunction(torch.autograd.Function):
             if need_dW:
                 dW = be.gemm(X.t(), S, precision=ctx.precision)[:, :fout].contiguous()
                 dW = graph.all_reduce_sum(dW)
-            if need_dX:
-                dX = be.gemm(S, _pad_cols(W, ctx.width).t(), precision=ctx.precision)
+            if need_dX:  # the gate rides in the GEMM's store
+                dX = be.gemm(S, _pad_cols(W, ctx.width).t(), precision=ctx.precision, gate=X if gate_dx else None)
         else:
             AX = saved[3]
             if need_dW:
@@ -353,7 +357,9 @@ class DistGCNConvFunction(torch.autograd.Function):
             if need_dX:
                 T = be.gemm(G, W.t(), precision=ctx.precision)
                 dX = graph.aggregate(T, tag="b")
-        return dX, None, dW, None, db, None, None
+                if gate_dx:  # the aggregation ends in an exchange or an accumulate: gate in a pass of its own
+                    dX = be.relu_backward(dX, X)
+        return dX, None, dW, None, db, None, None, None
 
 
 class DistGCN(torch.nn.Module):
@@ -362,10 +368,12 @@ class DistGCN(torch.nn.Module):
     layers but the last, log_softmax on top.  Every rank must construct it with
     the same RNG state so the weight replicas agree."""
 
-    def __init__(self, dims, *, precision: Optional[str] = None):
+    def __init__(self, dims, *, precision: Optional[str] = None, fuse_relu_backward: bool = True):
         super().__init__()
         import math
         self.precision = precision
+        # as in models.GCN: a hidden layer's ReLU backward is applied where the layer above produces its input gradient
+        self.fuse_relu_backward = fuse_relu_backward
         self.weights = torch.nn.ParameterList()
         for i in range(len(dims) - 1):
             s = math.sqrt(2.0 / (dims[i] + dims[i + 1]))
@@ -377,6 +385,9 @@ class DistGCN(torch.nn.Module):
         h = X_local
         last = len(self.weights) - 1
         for i, W in enumerate(self.weights):
+            fuse = 0
+            if self.fuse_relu_backward:
+                fuse = (1 if i < last else 0) | (2 if i > 0 else 0)  # every layer but the last has a ReLU
             h = DistGCNConvFunction.apply(h, graph, W, i < last, None, self.precision,
-                                          X_gathered if i == 0 else None)
+                                          X_gathered if i == 0 else None, fuse)
         return torch.log_softmax(h, dim=1) if log_softmax else h

@@ -37,12 +37,14 @@ class TorchCPUBackend:
             return out
         return y
 
-    def gemm(self, A, B, *, bias=None, relu=False, precision=None):
+    def gemm(self, A, B, *, bias=None, relu=False, precision=None, gate=None):
         y = A @ B
         if bias is not None:
             y = y + bias
         if relu:
             y = y * (y > 0)
+        if gate is not None:
+            y = y * (gate > 0)
         return y
 
     def relu_backward(self, dY, Y):
@@ -94,7 +96,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, n, dims, q, mode="rows"):
+def _worker(rank, world, port, n, dims, q, mode="rows", fuse=True):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -111,7 +113,7 @@ def _worker(rank, world, port, n, dims, q, mode="rows"):
             graph = FeatureShardedGraph(be.make_adj(rowptr, col, val, (n, n)), n, backend=be)
         lo, hi = graph.lo, graph.hi
         torch.manual_seed(5)
-        model = DistGCN(dims)
+        model = DistGCN(dims, fuse_relu_backward=fuse)
         Xl = X[lo:hi].clone().requires_grad_()
         # constant input features: exchanged once, outside the step
         Xg = graph.prepare_constant(X[lo:hi])
@@ -126,12 +128,14 @@ def _worker(rank, world, port, n, dims, q, mode="rows"):
 
 
 @pytest.mark.parametrize("world,n,dims", [(2, 64, [12, 20, 20, 5]), (3, 50, [9, 16, 4]), (2, 33, [20, 8, 6])])
-@pytest.mark.parametrize("mode", ["rows", "features"])
-def test_partitioned_model_matches_single_process(world, n, dims, mode):
+@pytest.mark.parametrize("mode,fuse", [("rows", True), ("features", True), ("rows", False)])
+def test_partitioned_model_matches_single_process(world, n, dims, mode, fuse):
+    """fuse: the ReLU backward of a hidden layer applied where the layer above produces its input gradient
+    (in the GEMM's store, or in a pass after the aggregation's exchange), or as the reference places it."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode, fuse)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]
