@@ -187,6 +187,9 @@ def cpu_reference_epoch_ms(cfg, sample_div: int, steps: int, warmup: int):
     from graphcuda_b200 import synth
     from oracle import gcn_oracle as O
     from oracle import ref_loader
+    # all the host threads this process may use (a launcher may have exported OMP_NUM_THREADS=1 for its workers)
+    avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, avail))
     kind = "port"
     ops = None
     if ref_loader.ref_ext_available():
