@@ -104,3 +104,28 @@ def test_precision_resolution_is_host_logic():
     assert L.gc_gemm_resolve_precision(1, 0, 256, 256, 2449029, 256, 256, 256, P.PREC_AUTO) == P.PREC_TF32X3
     assert L.gc_gemm_resolve_precision(1, 0, 256, 47, 2449029, 256, 47, 47, P.PREC_AUTO) == P.PREC_FP32_SIMT
     assert L.gc_gemm_resolve_precision(0, 0, 8192, 8192, 8192, 8192, 8192, 8192, P.PREC_FP32_SIMT) == P.PREC_FP32_SIMT
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 and a C program must link and call it."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "probe.c"
+    src.write_text(
+        '#include "graphcuda_b200.h"\n#include <stdio.h>\n'
+        "int main(void) {\n"
+        "  /* argument errors are reported without touching a device */\n"
+        "  int rc = gc_gemm_f32(0, 0, -1, 4, 4, 0, 4, 0, 4, 0, 4, 0, 0, 0, 0, GC_PREC_AUTO, 0, 0, 0);\n"
+        '  printf("%d %d %s\\n", gc_abi_version(), rc, gc_status_string(rc));\n'
+        "  return rc == GC_ERR_INVALID ? 0 : 1;\n}\n")
+    exe = tmp_path / "probe"
+    libdir = os.path.dirname(build.lib_path())
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe),
+                        "-L", libdir, "-lgraphcuda_b200", f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert run.stdout.split()[0] == str(_lib.lib().gc_abi_version())
