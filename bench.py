@@ -54,13 +54,15 @@ def parse():
     ap.add_argument("--partition", default="auto", choices=["auto", "features", "rows"],
                     help="multi-GPU scheme: aggregation sharded over feature columns (all-to-all) or adjacency rows "
                          "(all-gather); auto = rows up to 4 GPUs, features from 8 (measured cross-over)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="skip the untimed CPU float64 check of the benchmarked graph's layers (profiler captures)")
     ap.add_argument("--profile-warmup", action="store_true",
                     help="honour --warmup below 3 (profiler captures only; such a run is not a benchmark)")
     return ap.parse_args()
 
 
 def workload(shrink: int):
-    from graphcuda_b200 import synth
+    synth = _load_synth()
     cfg = dict(synth.CONFIGS["rmat_products"])
     if shrink > 1:
         cfg["nodes"] //= shrink
@@ -180,16 +182,23 @@ def measured_peaks():
 
 
 # ---------------------------------------------------------------- CPU baseline (reference code)
-def cpu_reference_epoch_ms(cfg, sample_div: int, steps: int, warmup: int):
-    """The reference's own CPU path (its gcn.cpp compiled for CPU when present,
-    else the oracle restatement of it) on an R-MAT sample 1/sample_div the size,
-    time scaled by sample_div (work is linear in nodes and edges)."""
-    from graphcuda_b200 import synth
+def _load_synth():
+    """The seeded generators, loaded by file path: importing the package would load the CUDA library, and the
+    reference arm must run without any of this repository's kernels in the process."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_gc_synth", os.path.join(ROOT, "graphcuda_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _cpu_reference_sample(cfg, sample_div: int, steps: int, warmup: int, budget_s: float):
+    """ms per training step of the reference's CPU path (its gcn.cpp compiled for CPU when present, else the
+    restatement of it) on an R-MAT sample 1/sample_div the size of the workload (same generator, same average
+    degree, same 3-layer model).  Stops early when budget_s is used up; returns (ms, steps actually timed, kind)."""
+    synth = _load_synth()
     from oracle import gcn_oracle as O
     from oracle import ref_loader
-    # all the host threads this process may use (a launcher may have exported OMP_NUM_THREADS=1 for its workers)
-    avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    torch.set_num_threads(max(1, avail))
     kind = "port"
     ops = None
     if ref_loader.ref_ext_available():
@@ -216,16 +225,53 @@ def cpu_reference_epoch_ms(cfg, sample_div: int, steps: int, warmup: int):
         opt.step()
         return loss.item()
 
-    for _ in range(warmup):
+    t_begin = time.perf_counter()
+    for i in range(warmup):
         step()
+        if i >= 0 and time.perf_counter() - t_begin > budget_s / 3:
+            break
+    done = 0
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
-    ms = (time.perf_counter() - t0) * 1e3 / max(steps, 1)
-    sample = (f"R-MAT sample 1/{sample_div} of the workload ({n} nodes, {m} undirected edges, same degree, "
-              f"same 3-layer model, fwd+loss+bwd+Adam), {steps} timed steps after {warmup} warm-up, "
-              f"time x{sample_div}")
-    return ms * sample_div, kind, torch.get_num_threads(), sample
+        done += 1
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    ms = (time.perf_counter() - t0) * 1e3 / max(done, 1)
+    return ms, done, kind, n, m
+
+
+def cpu_reference_epoch_ms(cfg, sample_div: int, steps: int, warmup: int, check_div: int = 0,
+                           budget_s: float = 150.0):
+    """The reference's CPU path timed on a bounded sample and scaled to the full workload.
+
+    The main sample (1/sample_div) runs the requested steps; a second, larger sample (1/check_div, two steps)
+    measures how the time grows with the size, and the growth exponent p (time ~ size^p) found from the two
+    points is what the scaling to full size uses (p = 1 when no second sample is taken).  Returns a dict."""
+    # all the host threads this process may use (a launcher may have exported OMP_NUM_THREADS=1 for its workers)
+    avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, avail))
+    ms_a, done_a, kind, n_a, m_a = _cpu_reference_sample(cfg, sample_div, steps, warmup, budget_s)
+    p = 1.0
+    second = None
+    if check_div and check_div < sample_div:
+        ms_b, done_b, _, n_b, m_b = _cpu_reference_sample(cfg, check_div, 2, 1, budget_s)
+        import math
+        p = math.log(ms_b / ms_a) / math.log(sample_div / check_div)
+        second = {"div": check_div, "nodes": n_b, "undirected_edges": m_b, "ms_per_step": ms_b, "steps": done_b}
+        full = ms_b * (check_div ** p)
+    else:
+        full = ms_a * sample_div
+    sample = (f"R-MAT sample 1/{sample_div} of the workload ({n_a} nodes, {m_a} undirected edges, same degree, "
+              f"same 3-layer model, fwd+loss+bwd+Adam): {ms_a:.1f} ms per step over {done_a} timed steps")
+    if second:
+        sample += (f"; second sample 1/{check_div} ({second['nodes']} nodes): {second['ms_per_step']:.1f} ms per step "
+                   f"=> time ~ size^{p:.3f} (1.000 = linear); value = the 1/{check_div} time x {check_div}^{p:.3f}")
+    else:
+        sample += f"; value = that time x {sample_div} (work is linear in nodes and edges)"
+    return {"value": full, "unit": "ms", "cores": torch.get_num_threads(), "kind": kind, "sample": sample,
+            "extrapolated": True, "measured": {"div": sample_div, "ms_per_step": ms_a, "steps": done_a},
+            "second_point": second, "growth_exponent": p}
 
 
 def run_reference(args):
@@ -233,19 +279,40 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = workload(args.shrink)
-    # a bounded run: the sample is sized so that one step is a few seconds of CPU work
-    steps = max(1, min(args.steps, 5))
-    warm = max(1, min(args.warmup, 2))
-    ms, kind, cores, sample = cpu_reference_epoch_ms(cfg, args.cpu_sample_div, steps, warm)
+    # the sample is sized so that one step is a few seconds of CPU work; the requested step counts are honoured
+    # as far as they fit a bounded run (the line says how many steps were timed)
+    cb = cpu_reference_epoch_ms(cfg, args.cpu_sample_div, max(1, args.steps), max(1, args.warmup),
+                                check_div=max(1, args.cpu_sample_div // 4), budget_s=150.0)
+    ms = cb["value"]
+    done = cb["measured"]["steps"]
     line = {
-        "impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus, "steps": done,
+        "warmup": max(1, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": config_dict(cfg, args, 1),
-        "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": kind, "sample": sample},
+        "value_is": "extrapolated from bounded samples of the workload (see cpu_baseline.sample); "
+                    "the measured per-step times are in cpu_baseline.measured / second_point",
+        "steps_requested": args.steps, "steps_capped": done < args.steps,
+        "cpu_baseline": cb,
         "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "shared_objects_of_this_repo_loaded": _repo_shared_objects(),
     }
     print(json.dumps(line), flush=True)
+
+
+def _repo_shared_objects():
+    """Shared objects under this repository mapped into this process (the reference arm must show the
+    reference's CPU module only, never the CUDA library of the package)."""
+    found = set()
+    try:
+        for ln in open("/proc/self/maps"):
+            path = ln.split()[-1]
+            if path.startswith(ROOT) and ".so" in path:
+                found.add(os.path.relpath(path, ROOT))
+    except OSError:
+        pass
+    return sorted(found)
 
 
 def config_dict(cfg, args, world):
@@ -257,6 +324,88 @@ def config_dict(cfg, args, world):
         "precision": args.precision, "l2": "inputs larger than L2 (no flush needed)",
         "shrink": args.shrink,
     }
+
+
+# ---------------------------------------------------------------- parity (outside every timed region)
+PARITY_TOL = 1e-4
+
+
+def _cpu_rows_times_matrix(rows, rowptr, col, val, H):
+    """sum_j A[r, j] H[j, :] in float64 for the listed rows of a CSR matrix held on the CPU."""
+    out = torch.zeros(len(rows), H.size(1), dtype=torch.float64)
+    for i, r in enumerate(rows.tolist()):
+        s, e = int(rowptr[r]), int(rowptr[r + 1])
+        if e > s:
+            out[i] = val[s:e].double() @ H[col[s:e].long()].double()
+    return out
+
+
+def _rel_errs(out, ref):
+    out = out.double()
+    d = (out - ref)
+    return float(d.norm() / max(float(ref.norm()), 1e-300)), float(d.abs().max() / max(float(ref.abs().max()), 1e-300))
+
+
+def parity_block(model, X, y, graph, X_gathered, csr_host, n, world, rank, dev, gather_rows):
+    """Compares the training path on the benchmarked graph with the reference's layer formulas evaluated on the
+    CPU in float64 (src/graphcuda/cpp/gcn.cpp:10-15 forward, :34 weight gradient), layer by layer on the
+    layer's own input as the GPU produced it:
+      * forward: relu((A h_{l-1}) W_l) on ~1000 sampled rows (the highest- and lowest-degree rows, the rest
+        drawn at random over ALL ranks' rows);
+      * backward: the whole dW_1 = (A X)^T G_1 (a sum over every node, all-reduced over the ranks).
+    gather_rows(t) returns the full matrix (all ranks' row blocks) on every rank.  Runs once, untimed."""
+    import graphcuda_b200 as gc
+    for p_ in model.parameters():
+        p_.grad = None
+    if world == 1:
+        out, hs = model(X, graph, log_softmax=False, return_hidden=True)
+    else:
+        out, hs = model(X, graph, X_gathered=X_gathered, log_softmax=False, return_hidden=True)
+    for h in hs[1:]:
+        h.retain_grad()
+    loss = gc.log_softmax_nll_loss(out, y, scale=1.0 / n)
+    loss.backward()
+    weights = [p_.detach() for p_ in model.parameters()]
+    full = [gather_rows(h.detach()) for h in hs]
+    G1 = gather_rows((hs[1].grad * (hs[1].detach() > 0)).contiguous())  # gated gradient of layer 1 (idempotent)
+    dW1 = list(model.parameters())[0].grad.detach().clone()
+    res = None
+    if rank == 0:
+        rowptr, col, val = csr_host
+        deg = (rowptr[1:] - rowptr[:-1])
+        order = torch.argsort(deg, descending=True, stable=True)
+        g = torch.Generator().manual_seed(123)
+        rows = torch.cat([order[:16], order[-16:], torch.randint(0, n, (992,), generator=g)]).unique()
+        layers = {}
+        worst = 0.0
+        for l, W in enumerate(weights):
+            Hprev = full[l].cpu()
+            ref = _cpu_rows_times_matrix(rows, rowptr, col, val, Hprev) @ W.double().cpu()
+            if l < len(weights) - 1:
+                ref = ref * (ref > 0)
+            fro, mx = _rel_errs(full[l + 1][rows.to(dev)].cpu(), ref)
+            layers[f"layer{l + 1}_forward"] = {"rel_fro": fro, "rel_max": mx, "rows": int(rows.numel())}
+            worst = max(worst, fro, mx)
+            del Hprev
+        # dW of the first layer over every node: (A X)^T G in float32 blocks summed in float64
+        A = torch.sparse_csr_tensor(rowptr.long(), col.long(), val, size=(n, n))
+        AX = A @ full[0].cpu()
+        Gc = G1.cpu()
+        acc = torch.zeros(AX.size(1), Gc.size(1), dtype=torch.float64)
+        for s0 in range(0, n, 1 << 16):
+            acc += (AX[s0:s0 + (1 << 16)].t() @ Gc[s0:s0 + (1 << 16)]).double()
+        fro, mx = _rel_errs(dW1.cpu(), acc)
+        layers["layer1_weight_gradient"] = {"rel_fro": fro, "rel_max": mx, "rows": n}
+        worst = max(worst, fro, mx)
+        res = {"ok": bool(worst < PARITY_TOL), "tolerance": PARITY_TOL, "max_rel_err": worst, "checks": layers,
+               "reference": "CPU float64 evaluation of relu((A h) W) and (A X)^T G on the GPU's own layer inputs, "
+                            "sampled rows over all ranks (forward) / all rows (weight gradient)",
+               "loss": float(loss.item())}
+    else:
+        float(loss.item())
+    for p_ in model.parameters():
+        p_.grad = None
+    return res
 
 
 # ---------------------------------------------------------------- our arm
@@ -288,7 +437,9 @@ def run_ours(args):
     edges = synth.rmat_edges(cfg["scale"], n, cfg["edges"], cfg["seed"], device=dev)
     adj = gc.normalized_adjacency(synth.symmetrize(edges), n, symmetric=True)
     del edges
-    X_full_host = None
+    csr_host = None
+    if rank == 0 and not args.no_parity:  # the checker's copy of the graph (host memory)
+        csr_host = (adj.rowptr.cpu().long(), adj.col.cpu(), adj.val.cpu())
     part = None
     if world == 1:
         X = synth.normal_features(n, DIMS[0], seed=11, device=dev)
@@ -374,6 +525,39 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     final_loss = float(loss.item())
 
+    # ---- parity, untimed: the layers of THIS graph against the reference's formulas on the CPU, and a probe of
+    # the logits of 64 fixed nodes (spread over all ranks' rows) that lines run at different N can be compared on
+    def gather_rows(t):
+        if world == 1:
+            return t
+        B = part.part.block
+        src = torch.zeros((B, t.size(1)), dtype=t.dtype, device=dev)
+        src[:t.size(0)].copy_(t)
+        full = torch.empty((B * world, t.size(1)), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(full, src)
+        return full[:n]
+
+    probe_rows = torch.linspace(0, n - 1, 64).long()
+    with torch.no_grad():
+        logits = (model(X, adj, log_softmax=False) if world == 1
+                  else model(X, part, X_gathered=X_gathered, log_softmax=False))
+        lo_r = 0 if world == 1 else part.lo
+        mine = (probe_rows >= lo_r) & (probe_rows < lo_r + logits.size(0))
+        probe = torch.zeros((64, DIMS[-1]), dtype=torch.float32, device=dev)
+        probe[mine.to(dev)] = logits[(probe_rows[mine] - lo_r).to(dev)]
+        if world > 1:
+            dist.all_reduce(probe)
+        del logits
+    logits_probe = {"rows": "64 nodes, torch.linspace(0, n-1, 64)", "after_steps": n_warm + args.steps,
+                    "sum": float(probe.double().sum().item()), "abs_sum": float(probe.double().abs().sum().item()),
+                    "first_row": [round(float(v), 6) for v in probe[0].tolist()[:8]],
+                    "l2": float(probe.double().norm().item())}
+    parity = None
+    if not args.no_parity:
+        parity = parity_block(model, X, y, adj if world == 1 else part, X_gathered, csr_host, n, world, rank, dev,
+                              gather_rows)
+        barrier()
+
     # ---- end to end: pinned host inputs copied in, loss read back, every step ----
     Xh = X.cpu().pin_memory()
     yh = y.cpu().pin_memory()
@@ -443,6 +627,8 @@ def run_ours(args):
                        "in flight while step i computes, the first copy of the timed region is exposed",
                 "value_without_prefetch": e2e_times[False]},
         "gpu_launches": int(launches), "clocks": clocks, "final_loss": final_loss, "setup_s": setup_s,
+        "partition": (args.partition if world > 1 else "none"),
+        "parity": parity, "logits_probe": logits_probe,
         "spmm_gbs": achieved, "spmm_pct_hbm_peak": 100.0 * achieved / peak,
     }
 
@@ -455,8 +641,7 @@ def run_ours(args):
         except Exception as ex:  # auxiliary numbers never take the headline down
             line["aux"] = {"error": repr(ex)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        ms, kind, cores, sample = cpu_reference_epoch_ms(cfg, args.cpu_sample_div, 2, 1)
-        line["cpu_baseline"] = {"value": ms, "unit": "ms", "cores": cores, "kind": kind, "sample": sample}
+        line["cpu_baseline"] = cpu_reference_epoch_ms(cfg, args.cpu_sample_div, 2, 1)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

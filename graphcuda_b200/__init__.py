@@ -17,7 +17,7 @@ if "graphcuda_b200.build" not in getattr(_sys, "orig_argv", []):
 from . import _graphcuda  # noqa: E402
 from ._graphcuda import (gemm_cublas, matmul1, matmul2, matmul3, matmul4,  # noqa: E402
                          spmm_cusparse)
-from .adjacency import (CSRAdjacency, DenseAdjacency, as_adjacency, gcn_norm,  # noqa: E402
+from .adjacency import (CSRAdjacency, DenseAdjacency, as_adjacency, degree_order, gcn_norm,  # noqa: E402
                         normalized_adjacency)
 from .gcn import GCNConv, GCNConvFunction  # noqa: E402
 from .feed import PinnedFeed  # noqa: E402

@@ -33,8 +33,10 @@ SIGNATURES = {
     "gc_spmm_plan_build": (_int, [_i32p, _i32p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _void, _size, _void, _size,
                                   _void]),
     "gc_spmm_scratch_bytes": (_size, [_i64, _i64]),
+    "gc_spmm_plan_check": (_int, [_void, _i64, _i64, _i64, _void]),
     "gc_spmm_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p, _i64,
-                               _f32p, _f32p, _void, _i64, _i64, _void, _size, _void]),
+                               _f32p, _f32p, _void, _i64, _i64, _i64, _void, _size, _void]),
+    "gc_gather_sum_f32": (_int, [_f32p, _i64, _i64, _i64, _i32p, _i64, _i64, _f32p, _i64, _int, _void]),
     "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
                                        _i64, _f32p, _f32p, _void, _i64, _i64, _i64, _void]),
     "gc_gemm_workspace_bytes": (_size, [_int, _int, _i64, _i64, _i64, _int]),

@@ -49,6 +49,8 @@ class CSRAdjacency:
         self._symmetric = symmetric
         self.use_plan = bool(build_plan)
         self.segment = None  # longest piece in non-zeros; None: gc_spmm_default_segment(nnz)
+        self.perm = None  # set by normalized_adjacency(reorder=...): perm[new] = old vertex id
+        self.inv_perm = None
         self._plans = {}  # panel_cols -> SpmmPlan
 
     def plan_for(self, F: int, panel_cols: Optional[int] = None):
@@ -155,7 +157,8 @@ class CSRAdjacency:
                                    out.data_ptr(), ldy, mask.data_ptr() if mask is not None else None,
                                    gate.data_ptr() if gate is not None else None,
                                    plan.buf.data_ptr() if plan is not None else None,
-                                   plan.n_pieces if plan is not None else 0, plan.n_cut if plan is not None else 0,
+                                   plan.n_pieces if plan is not None else 0, plan.n_slots if plan is not None else 0,
+                                   plan.n_cut if plan is not None else 0,
                                    scratch.data_ptr() if scratch is not None else None,
                                    scratch.numel() if scratch is not None else 0, _stream(dev))
         _lib.check(st, "gc_spmm_csr_f32")
@@ -181,8 +184,18 @@ class DenseAdjacency:
 
     @property
     def symmetric(self) -> bool:
+        """A == A^T bit for bit.  The verdict is remembered on the tensor itself (with the version it was taken
+        at), so wrapping the same matrix again -- every layer call does -- does not repeat the comparison."""
         if self._symmetric is None:
-            self._symmetric = self.shape[0] == self.shape[1] and bool(torch.equal(self.A, self.A.t()))
+            memo = getattr(self.A, "_gc_symmetric", None)
+            if memo is not None and memo[0] == self.A._version:
+                self._symmetric = memo[1]
+            else:
+                self._symmetric = self.shape[0] == self.shape[1] and bool(torch.equal(self.A, self.A.t()))
+                try:
+                    self.A._gc_symmetric = (self.A._version, self._symmetric)
+                except Exception:
+                    pass
         return self._symmetric
 
     def matmul(self, H: torch.Tensor, *, bias=None, relu=False, want_mask=False, accumulate_into=None, out=None,
@@ -225,7 +238,7 @@ def _cache_key(t: torch.Tensor):
         v = t.values()
         return ("csr", v.data_ptr(), t.crow_indices().data_ptr(), t.col_indices().data_ptr(), v._version,
                 tuple(t.shape))
-    return ("dense", t.data_ptr(), t._version, tuple(t.shape), t.stride())
+    raise RuntimeError(f"unsupported adjacency layout {t.layout}")
 
 
 def as_adjacency(adjm, *, symmetric: Optional[bool] = None):
@@ -246,6 +259,9 @@ def as_adjacency(adjm, *, symmetric: Optional[bool] = None):
     _require(adjm.dim() == 2, "A must be 2D")
     _require(adjm.is_cuda, "A and B must be CUDA tensors")
     _require(adjm.dtype == torch.float32, "A values must be float32")
+    if adjm.layout == torch.strided:
+        # not cached: the wrapper holds the matrix itself, so a cache entry would pin an N x N buffer for good
+        return DenseAdjacency(adjm, symmetric=symmetric)
     key = _cache_key(adjm)
     with _cache_lock:
         hit = _cache.get(key)
@@ -259,8 +275,6 @@ def as_adjacency(adjm, *, symmetric: Optional[bool] = None):
     elif adjm.layout == torch.sparse_csr:
         adj = CSRAdjacency(adjm.crow_indices().to(torch.int32), adjm.col_indices().to(torch.int32), adjm.values(),
                            adjm.shape, symmetric=symmetric)
-    elif adjm.layout == torch.strided:
-        adj = DenseAdjacency(adjm, symmetric=symmetric)
     else:
         raise RuntimeError(f"unsupported adjacency layout {adjm.layout}")
     with _cache_lock:
@@ -301,14 +315,42 @@ def gcn_norm(edge_index: torch.Tensor, num_nodes: int) -> torch.Tensor:
     return w
 
 
+def degree_order(edge_index: torch.Tensor, num_nodes: int):
+    """Vertex relabelling by decreasing degree (ties: lower old id first).
+
+    Returns (perm, inv): perm[new] = old, inv[old] = new.  The degree is the
+    number of edges whose target (edge_index[1]) is the vertex, as gcn_norm
+    counts it.  In the relabelled graph the heavy vertices are the low ids, so
+    the rows of a feature matrix that most gathers hit are contiguous."""
+    _require(edge_index.dtype == torch.int64 and edge_index.dim() == 2 and edge_index.size(0) == 2,
+             "edge_index must be an int64 [2, E] tensor")
+    deg = torch.bincount(edge_index[1], minlength=num_nodes)
+    perm = torch.argsort(deg, descending=True, stable=True)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(num_nodes, device=perm.device, dtype=perm.dtype)
+    return perm, inv
+
+
 def normalized_adjacency(edge_index: torch.Tensor, num_nodes: int, *, add_self_loops: bool = True,
-                         symmetric: Optional[bool] = None) -> CSRAdjacency:
+                         symmetric: Optional[bool] = None, reorder: Optional[str] = None) -> CSRAdjacency:
     """Edge list -> (+self-loops) -> symmetric normalisation -> coalesced int32
     CSR, the whole preprocessing of tests/gcn/graphcuda_impl.py:27-38 on the
     GPU.  The (row, col) ordering uses torch.sort on the device; degree,
     normalisation, de-duplication and CSR assembly are this library's kernels.
+
+    reorder="degree": the vertices are first relabelled by decreasing degree
+    (degree_order); the result is the adjacency of the relabelled graph and
+    carries ``perm`` (perm[new] = old) and ``inv_perm``.  Feature and label
+    rows must be permuted the same way (``X[adj.perm]``); outputs come back in
+    the new order (``Y_old = Y[adj.inv_perm]``).
     """
     _require(edge_index.is_cuda and edge_index.dtype == torch.int64, "edge_index must be a CUDA int64 tensor")
+    _require(reorder in (None, "degree"), "reorder must be None or 'degree'")
+    if reorder == "degree":
+        perm, inv = degree_order(edge_index, num_nodes)  # self-loops add one to every degree: same order
+        adj = normalized_adjacency(inv[edge_index], num_nodes, add_self_loops=add_self_loops, symmetric=symmetric)
+        adj.perm, adj.inv_perm = perm, inv
+        return adj
     dev = edge_index.device
     if add_self_loops:
         loops = torch.arange(num_nodes, device=dev, dtype=torch.int64)

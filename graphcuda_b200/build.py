@@ -26,6 +26,7 @@ LIBNAME = "libgraphcuda_b200.so"
 SOURCES = [
     "abi.cu",
     "spmm_csr.cu",
+    "gather_probe.cu",
     "gemm.cu",
     "gemm_simt.cu",
     "gemm_tcgen05.cu",

@@ -26,7 +26,7 @@ int fail(int code, const char* fmt, ...) {
 
 extern "C" {
 
-int gc_abi_version(void) { return 2; }
+int gc_abi_version(void) { return 3; }
 
 long long gc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

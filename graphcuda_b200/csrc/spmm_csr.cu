@@ -45,7 +45,8 @@ struct PlanHeader {
   int32_t n_slots;   // partial-sum rows in scratch (pieces of cut rows)
   int32_t n_cut;     // rows that were cut
   int32_t panel_cols;
-  int32_t pad[2];
+  int32_t overflow;  // sticky: a launch found less scratch than the plan's partial sums need and skipped some
+  int32_t pad;
 };
 constexpr int32_t kPlanMagic = 0x47435032;  // "GCP2"
 
@@ -155,7 +156,8 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
                    const float* __restrict__ val, int n_pieces, const int32_t* __restrict__ p_start,
                    const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
                    const float* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
-                   float* __restrict__ scratch, int64_t ldS, int slot_capacity, Epilogue ep) {
+                   float* __restrict__ scratch, int64_t ldS, int slot_capacity, int32_t* __restrict__ overflow,
+                   Epilogue ep) {
   using V = Vec<VW>;
   constexpr int PIECES_PER_CTA = 256 / GROUP;
   constexpr int PASS = GROUP * NACC * VW;
@@ -176,7 +178,10 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
     target = v;
   }
   const bool direct = target >= 0;
-  if (!direct && (~target) >= slot_capacity) return;  // never write past the caller's scratch
+  if (!direct && (~target) >= slot_capacity) {  // never write past the caller's scratch; leave a trace instead
+    if (lane_g == 0) *overflow = 1;
+    return;
+  }
   float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
   float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
   const float* grow = (direct && ep.gate) ? ep.gate + int64_t(target) * ldY : nullptr;
@@ -249,7 +254,8 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
                           const float* __restrict__ val, int n_pieces, const int32_t* __restrict__ p_start,
                           const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
                           const float* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
-                          float* __restrict__ scratch, int64_t ldS, int slot_capacity, Epilogue ep) {
+                          float* __restrict__ scratch, int64_t ldS, int slot_capacity,
+                          int32_t* __restrict__ overflow, Epilogue ep) {
   constexpr int G = 8;
   const int lane_g = threadIdx.x % G;
   const int v = blockIdx.x * (256 / G) + threadIdx.x / G;
@@ -266,7 +272,10 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
     target = v;
   }
   const bool direct = target >= 0;
-  if (!direct && (~target) >= slot_capacity) return;
+  if (!direct && (~target) >= slot_capacity) {
+    if (lane_g == 0) *overflow = 1;
+    return;
+  }
   const int units = F / 4;
   float4 acc[NV];
 #pragma unroll
@@ -324,14 +333,17 @@ template <int VW>
 __global__ void __launch_bounds__(256)
 spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, const int32_t* __restrict__ cut_slot0,
                      const int32_t* __restrict__ cut_nslots, const float* __restrict__ scratch, int64_t ldS,
-                     int slot_capacity, float* __restrict__ Y, int64_t ldY, Epilogue ep) {
+                     int slot_capacity, int32_t* __restrict__ overflow, float* __restrict__ Y, int64_t ldY,
+                     Epilogue ep) {
   using V = Vec<VW>;
   const int lane = threadIdx.x % 32;
   const int warps = gridDim.x * 8;
   for (int i = blockIdx.x * 8 + threadIdx.x / 32; i < n_cut; i += warps) {
     const int row = __ldg(cut_row + i);
     const int s0 = __ldg(cut_slot0 + i);
-    const int s1 = min(s0 + __ldg(cut_nslots + i), slot_capacity);
+    const int s_end = s0 + __ldg(cut_nslots + i);
+    const int s1 = min(s_end, slot_capacity);
+    if (s_end > slot_capacity && lane == 0) *overflow = 1;
     float* yrow = Y + int64_t(row) * ldY;
     float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
     const float* grow = ep.gate ? ep.gate + int64_t(row) * ldY : nullptr;
@@ -463,7 +475,8 @@ __global__ void plan_header_kernel(PlanHeader* hdr, int M, int n_pieces, int n_s
   hdr->n_slots = n_slots;
   hdr->n_cut = n_cut;
   hdr->panel_cols = panel_cols;
-  hdr->pad[0] = hdr->pad[1] = 0;
+  hdr->overflow = 0;
+  hdr->pad = 0;
 }
 
 // Workspace carve-up shared by the count and build steps.
@@ -547,29 +560,29 @@ constexpr int pieces_min_ctas(int group, int nacc, int vw) { return (vw == 4 && 
 template <int GROUP, int NACC, int VW, int U>
 void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                    const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
-                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
                    cudaStream_t st) {
   constexpr int PER_CTA = 256 / GROUP;
   const unsigned grid = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
   constexpr int MINB = pieces_min_ctas(GROUP, NACC, VW);
   if (planned)
     spmm_pieces_kernel<GROUP, NACC, VW, U, true, MINB>
-        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ep);
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep);
   else
     spmm_pieces_kernel<GROUP, NACC, VW, U, false, MINB>
-        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ep);
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep);
 }
 
 #define GC_PIECES(G, A, VWID, UU)                                                                                 \
   launch_pieces<G, A, VWID, UU>(planned, rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, \
-                                cap, ep, st)
+                                cap, ovf, ep, st)
 
 // GROUP x NACC 128-bit vectors cover a row of H; small groups keep several
 // pieces in flight per warp and four accumulators per lane amortise the
 // (col, val) broadcast.
 void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                    const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
-                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
                    cudaStream_t st) {
   const int units = F / 4;  // 128-bit vectors per row
   // Measured on the 126 M-non-zero graph: up to 8 floats the lane-per-non-zero kernel wins (F = 8: 0.99 ms
@@ -582,10 +595,10 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
   do {                                                                                                          \
     if (planned)                                                                                                \
       spmm_pieces_narrow_kernel<NV, UU, true><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, \
-                                                                   ldH, Y, ldY, scratch, ldS, cap, ep);         \
+                                                                   ldH, Y, ldY, scratch, ldS, cap, ovf, ep);    \
     else                                                                                                        \
       spmm_pieces_narrow_kernel<NV, UU, false><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F,  \
-                                                                    H, ldH, Y, ldY, scratch, ldS, cap, ep);     \
+                                                                    H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep); \
   } while (0)
     if (units <= 1) GC_NARROW(1, 4);
     else GC_NARROW(2, 4);
@@ -603,7 +616,7 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
 
 void dispatch_scalar(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                      const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
-                     float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, const Epilogue& ep,
+                     float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
                      cudaStream_t st) {
   if (F <= 8) GC_PIECES(8, 1, 1, 4);
   else if (F <= 16) GC_PIECES(16, 1, 1, 4);
@@ -722,9 +735,28 @@ size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F) {
   return std::max<size_t>(size_t(n_slots) * size_t(scratch_ld(F)) * sizeof(float), 256);
 }
 
+int gc_spmm_plan_check(const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* stream) {
+  GC_REQUIRE(plan, "gc_spmm_plan_check: null plan");
+  cudaStream_t st = gc::as_stream(stream);
+  PlanHeader h{};
+  cudaError_t e = cudaMemcpyAsync(&h, plan, sizeof(h), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return gc::fail(GC_ERR_CUDA, "gc_spmm_plan_check: %s", cudaGetErrorString(e));
+  if (h.magic != kPlanMagic) return gc::fail(GC_ERR_INVALID, "gc_spmm_plan_check: not a plan built by this library");
+  if (h.n_pieces != n_pieces || h.n_slots != n_slots || h.n_cut != n_cut)
+    return gc::fail(GC_ERR_INVALID,
+                    "gc_spmm_plan_check: the plan holds %d pieces / %d slots / %d cut rows, the caller passed "
+                    "%lld / %lld / %lld",
+                    h.n_pieces, h.n_slots, h.n_cut, (long long)n_pieces, (long long)n_slots, (long long)n_cut);
+  if (h.overflow)
+    return gc::fail(GC_ERR_DEVICE_FLAG,
+                    "gc_spmm_plan_check: a launch on this plan skipped partial sums (counts or scratch too small)");
+  return GC_OK;
+}
+
 int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
                     const float* H, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
-                    float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_cut,
+                    float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
                     void* scratch, size_t scratch_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && F >= 0, "gc_spmm_csr_f32: negative size");
   GC_REQUIRE(M < INT32_MAX && K < INT32_MAX && F < INT32_MAX, "gc_spmm_csr_f32: size out of int32 range");
@@ -743,12 +775,15 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
   const int32_t *ps = nullptr, *pl = nullptr, *pt = nullptr;
   PlanView pv{};
   int np = int(M), cap = 0;
+  int32_t* ovf = nullptr;
   const int64_t ldS = scratch_ld(F);
   if (planned) {
     GC_REQUIRE(gc::aligned16(plan), "gc_spmm_csr_f32: plan must be 16-byte aligned");
-    GC_REQUIRE(n_pieces >= M && n_pieces < INT32_MAX && n_cut >= 0 && n_cut <= M,
-               "gc_spmm_csr_f32: n_pieces / n_cut do not describe a plan of this matrix");
+    GC_REQUIRE(n_pieces >= M && n_pieces < INT32_MAX && n_cut >= 0 && n_cut <= M && n_slots >= 0 &&
+                   n_slots <= n_pieces && (n_cut == 0) == (n_slots == 0) && n_slots >= 2 * n_cut,
+               "gc_spmm_csr_f32: n_pieces / n_slots / n_cut do not describe a plan of this matrix");
     pv = plan_view(const_cast<void*>(plan), n_pieces, n_cut);
+    ovf = &pv.hdr->overflow;  // the one word of the plan a launch may write
     ps = pv.start;
     pl = pv.len;
     pt = pv.target;
@@ -756,26 +791,29 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
     if (n_cut > 0) {
       if (!scratch) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: the plan cuts rows but scratch is null");
       GC_REQUIRE(gc::aligned16(scratch), "gc_spmm_csr_f32: scratch must be 16-byte aligned");
-      const size_t rows = scratch_bytes / (size_t(ldS) * sizeof(float));
-      cap = rows > size_t(INT32_MAX) ? INT32_MAX : int(rows);
-      if (cap < 1) return gc::fail(GC_ERR_WORKSPACE, "gc_spmm_csr_f32: scratch too small");
+      const size_t need = gc_spmm_scratch_bytes(n_slots, F);
+      if (scratch_bytes < need)
+        return gc::fail(GC_ERR_WORKSPACE,
+                        "gc_spmm_csr_f32: %lld partial-sum rows of F=%lld need %zu bytes of scratch, got %zu",
+                        (long long)n_slots, (long long)F, need, scratch_bytes);
+      cap = int(n_slots);  // slots beyond what the caller declared are skipped and flagged, never written
     }
   }
   float* sc = static_cast<float*>(scratch);
   if (vec4)
-    dispatch_vec4(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ep, st);
+    dispatch_vec4(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, st);
   else
-    dispatch_scalar(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ep, st);
+    dispatch_scalar(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, st);
   int rc = gc::check_launch("gc_spmm_csr_f32 (pieces)");
   if (rc != GC_OK) return rc;
   if (planned && n_cut > 0) {
     const unsigned g = unsigned(std::min<int64_t>((n_cut + 7) / 8, gc::kNumSMs * 8));
     if (vec4)
       spmm_finalize_kernel<4><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
-                                                 cap, Y, ldY, ep);
+                                                 cap, ovf, Y, ldY, ep);
     else
       spmm_finalize_kernel<1><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
-                                                 cap, Y, ldY, ep);
+                                                 cap, ovf, Y, ldY, ep);
     rc = gc::check_launch("gc_spmm_csr_f32 (finalize)");
   }
   return rc;
@@ -821,7 +859,7 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
   GC_REQUIRE(n_slots >= 0, "gc_spmm_csr_f32_noalloc: negative n_slots");
   if (!plan || n_cut == 0)  // no cut rows, hence no scratch at all
     return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, gate, plan, n_pieces,
-                           n_cut, nullptr, 0, stream);
+                           n_slots, n_cut, nullptr, 0, stream);
   const size_t need = gc_spmm_scratch_bytes(n_slots, F);
   if (need > size_t(GC_SPMM_STATIC_SCRATCH_BYTES))
     return gc::fail(GC_ERR_WORKSPACE,
@@ -835,7 +873,7 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
   // piece pass of the same call, so stale contents of the shared buffer are
   // never observed and nothing has to be cleared.
   return gc_spmm_csr_f32(rowptr, col, val, M, K, F, H, ldH, bias, epilogue, Y, ldY, mask, gate, plan, n_pieces,
-                         n_cut, scratch, size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
+                         n_slots, n_cut, scratch, size_t(GC_SPMM_STATIC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

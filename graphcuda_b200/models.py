@@ -25,12 +25,17 @@ class GCN(torch.nn.Module):
                     lower.fuse_relu_backward |= 1
                     upper.fuse_relu_backward |= 2
 
-    def forward(self, x, adj, log_softmax: bool = True):
+    def forward(self, x, adj, log_softmax: bool = True, return_hidden: bool = False):
         """log_softmax=False returns the last layer's raw output, for
-        losses.log_softmax_nll_loss which fuses the normalisation with the loss."""
+        losses.log_softmax_nll_loss which fuses the normalisation with the loss.
+        return_hidden=True returns (output, [x, h1, ..., logits]): every layer's
+        input and output, for checks that compare layer by layer."""
+        hidden = [x]
         for conv in self.convs:
             x = conv(x, adj)
-        return torch.log_softmax(x, dim=1) if log_softmax else x
+            hidden.append(x)
+        out = torch.log_softmax(x, dim=1) if log_softmax else x
+        return (out, hidden) if return_hidden else out
 
     @torch.no_grad()
     def evaluate(self, x, adj, labels, masks=None):

@@ -31,26 +31,69 @@ from .engine import _pad_cols, _padded_width
 
 # ---------------------------------------------------------------- partition arithmetic
 class RowPartition:
-    """Uniform contiguous row blocks of size ceil(n / world); the last block may
-    be short (or empty)."""
+    """Contiguous row blocks, one per rank.
 
-    def __init__(self, n: int, world: int):
+    Without ``rowptr``: uniform blocks of ceil(n / world) rows; the last block
+    may be short (or empty).  With ``rowptr`` (the CSR row pointer of the matrix
+    being partitioned): block boundaries are placed so that every block carries
+    about nnz / world non-zeros -- what balances the aggregation when the vertex
+    labels are ordered by degree (adjacency.normalized_adjacency(reorder=
+    "degree")) and equal row counts would give the first rank most of the work.
+
+    Collectives move equal-sized blocks, so every block is padded to ``block``
+    rows (the largest block): "padded space" is the row numbering of the
+    gathered matrix, rank r's rows at [r * block, r * block + rows_r)."""
+
+    def __init__(self, n: int, world: int, *, rowptr: Optional[torch.Tensor] = None):
         if n < 0 or world < 1:
             raise ValueError("RowPartition: n >= 0 and world >= 1 required")
         self.n = n
         self.world = world
-        self.block = -(-n // world) if n else 0
+        if rowptr is None or n == 0:
+            self.block = -(-n // world) if n else 0
+            self.starts = [min(r * self.block, n) for r in range(world + 1)]
+            self.uniform = True
+        else:
+            if rowptr.numel() != n + 1:
+                raise ValueError("RowPartition: rowptr must have n + 1 entries")
+            rp = rowptr.detach().to("cpu", torch.int64)
+            nnz = int(rp[-1])
+            # first row whose prefix of non-zeros reaches r/world of the total
+            targets = torch.tensor([(nnz * r + world - 1) // world for r in range(1, world)], dtype=torch.int64)
+            cuts = torch.searchsorted(rp, targets, right=False).clamp_(0, n).tolist() if world > 1 else []
+            starts = [0] + cuts + [n]
+            for i in range(1, len(starts)):  # keep the boundaries monotone
+                starts[i] = max(starts[i], starts[i - 1])
+            self.starts = starts
+            self.block = max(b - a for a, b in zip(starts[:-1], starts[1:]))
+            self.uniform = False
         self.padded = self.block * world
 
     def bounds(self, rank: int):
         if not 0 <= rank < self.world:
             raise ValueError("rank out of range")
-        lo = min(rank * self.block, self.n)
-        hi = min(lo + self.block, self.n)
-        return lo, hi
+        return self.starts[rank], self.starts[rank + 1]
 
     def owner(self, row: int) -> int:
-        return row // self.block if self.block else 0
+        if self.uniform:
+            return row // self.block if self.block else 0
+        import bisect
+        return min(bisect.bisect_right(self.starts, row) - 1, self.world - 1)
+
+    def to_padded(self, ids: torch.Tensor) -> torch.Tensor:
+        """Global row / column ids -> positions in padded space (the identity for uniform blocks)."""
+        if self.uniform:
+            return ids
+        starts = torch.tensor(self.starts, dtype=torch.int64, device=ids.device)
+        own = torch.bucketize(ids.to(torch.int64), starts[1:-1].contiguous(), right=True)
+        return (own * self.block + (ids.to(torch.int64) - starts[own])).to(ids.dtype)
+
+    def unpad(self, full: torch.Tensor) -> torch.Tensor:
+        """Rows of a gathered matrix ([padded, F]) back in global order ([n, F])."""
+        if self.uniform:
+            return full[:self.n]
+        return torch.cat([full[r * self.block: r * self.block + (self.starts[r + 1] - self.starts[r])]
+                          for r in range(self.world)])
 
 
 def slice_csr_rows(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, lo: int, hi: int):
@@ -102,13 +145,25 @@ class PartitionedGraph:
     diagonal block and the remainder, plus the gather buffers."""
 
     def __init__(self, rowptr, col, val, n_nodes: int, *, rank: Optional[int] = None,
-                 world: Optional[int] = None, group=None, backend=None, rows_are_local: bool = False):
+                 world: Optional[int] = None, group=None, backend=None, rows_are_local: bool = False,
+                 balance: str = "rows", partition: Optional[RowPartition] = None):
         """rowptr/col/val: the GLOBAL CSR (every rank passes the same), or with
-        rows_are_local=True this rank's row block only (global column ids)."""
+        rows_are_local=True this rank's row block only (global column ids; pass
+        the `partition` it was cut with).  balance: "rows" = equal row counts,
+        "nnz" = equal non-zeros per rank (needs the global rowptr)."""
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
-        self.part = RowPartition(n_nodes, self.world)
+        if balance not in ("rows", "nnz"):
+            raise ValueError("balance must be 'rows' or 'nnz'")
+        if partition is not None:
+            self.part = partition
+        elif balance == "nnz":
+            if rows_are_local:
+                raise ValueError("balance='nnz' needs the global row pointer (or pass partition=)")
+            self.part = RowPartition(n_nodes, self.world, rowptr=rowptr)
+        else:
+            self.part = RowPartition(n_nodes, self.world)
         self.lo, self.hi = self.part.bounds(self.rank)
         self.n = n_nodes
         self.rows = self.hi - self.lo
@@ -117,6 +172,7 @@ class PartitionedGraph:
             rowptr, col, val = slice_csr_rows(rowptr, col, val, self.lo, self.hi)
         self.nnz_local_rows = int(col.numel())
         (rp_d, c_d, v_d), (rp_o, c_o, v_o) = split_csr_columns(rowptr, col, val, self.lo, self.hi)
+        c_o = self.part.to_padded(c_o)  # the remainder gathers from the all-gathered matrix (padded space)
         self.diag = self.backend.make_adj(rp_d, c_d, v_d, (self.rows, max(self.rows, 0)))
         self.offd = self.backend.make_adj(rp_o, c_o, v_o, (self.rows, self.part.padded))
         self.nnz_diag = int(c_d.numel())
@@ -267,8 +323,9 @@ class FeatureShardedGraph:
         w = Z_cols.size(1)
         recv = self._buf(("r2", w, tag), (P, B, w))
         self._all_to_all(recv, Z_cols.view(P, B, w))
-        out = recv.permute(1, 0, 2).reshape(B, P * w)
-        return out[:self.rows, :F].contiguous()
+        out = recv.permute(1, 0, 2).reshape(B, P * w)[:self.rows, :F]
+        # never hand out memory of the reusable receive buffer: the next exchange with this tag overwrites it
+        return out.clone() if out.untyped_storage().data_ptr() == recv.untyped_storage().data_ptr() else out.contiguous()
 
     def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
         """Column slab of a matrix that does not change between steps (the input
@@ -284,12 +341,57 @@ class FeatureShardedGraph:
         cols = gathered if gathered is not None else self.rows_to_columns(H_local, tag)
         b_slab = None
         if bias is not None:
-            bp = torch.zeros(self.world * w, dtype=torch.float32, device=self.device)
-            bp[:F] = bias
-            b_slab = bp[self.rank * w:(self.rank + 1) * w].contiguous()
+            bp = self._buf(("bias", w, tag), (self.world * w,))  # zero-filled once; the tail beyond F stays zero
+            bp[:F].copy_(bias)
+            b_slab = bp[self.rank * w:(self.rank + 1) * w]
         out = self._buf(("o", w, tag), (self.part.padded, w))
         self.backend.spmm(self.adj, cols[:self.n], bias=b_slab, relu=relu, out=out[:self.n])  # tail rows stay zero
         return self.columns_to_rows(out, F, tag)
+
+
+class HybridGraph:
+    """Both schemes behind one interface, chosen per aggregation by the width of
+    the matrix being aggregated.
+
+    The all-gather of the row partition delivers (P-1)/P of the matrix to every
+    rank, the two transposes of feature sharding move 2 (P-1)/P^2 of it but the
+    aggregation then walks ALL non-zeros on a slab of width F/P.  Narrow
+    matrices (the class logits and their gradients) are cheap to gather and
+    degenerate to a few columns per rank when sharded, wide ones (the hidden
+    width) are the other way round; constant inputs are gathered once and cost
+    no exchange at all in the row partition.  So: rows for F < wide_from and for
+    pre-gathered inputs, feature slabs for F >= wide_from.  Dense layers are
+    row-sharded in both, so the two can be mixed freely inside one model.
+    """
+
+    def __init__(self, rowptr, col, val, adj, n_nodes: int, *, rank: Optional[int] = None,
+                 world: Optional[int] = None, group=None, backend=None, device=None, wide_from: int = 128):
+        """rowptr/col/val: the global CSR (sliced into this rank's rows here);
+        adj: the same matrix as the backend's object (every rank holds it whole)."""
+        self.rows_graph = PartitionedGraph(rowptr, col, val, n_nodes, rank=rank, world=world, group=group,
+                                           backend=backend)
+        self.cols_graph = FeatureShardedGraph(adj, n_nodes, rank=rank, world=world, group=group, backend=backend,
+                                              device=device if device is not None else val.device)
+        g = self.rows_graph
+        self.group, self.rank, self.world, self.part = g.group, g.rank, g.world, g.part
+        self.lo, self.hi, self.rows, self.n = g.lo, g.hi, g.rows, g.n
+        self.backend = g.backend
+        self.device = g.device
+        self.wide_from = int(wide_from)
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        return self.rows_graph.all_reduce_sum(t)
+
+    def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
+        return self.rows_graph.prepare_constant(X_local)
+
+    def scheme_for(self, F: int, pre_gathered: bool) -> str:
+        return "rows" if (pre_gathered or F < self.wide_from or self.world == 1) else "features"
+
+    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a"):
+        if self.scheme_for(H_local.size(1), gathered is not None) == "rows":
+            return self.rows_graph.aggregate(H_local, gathered=gathered, bias=bias, relu=relu, tag=tag)
+        return self.cols_graph.aggregate(H_local, bias=bias, relu=relu, tag=tag)
 
 
 class DistGCNConvFunction(torch.autograd.Function):
@@ -348,8 +450,11 @@ class DistGCNConvFunction(torch.autograd.Function):
             if need_dW:
                 dW = be.gemm(X.t(), S, precision=ctx.precision)[:, :fout].contiguous()
                 dW = graph.all_reduce_sum(dW)
-            if need_dX:  # the gate rides in the GEMM's store
-                dX = be.gemm(S, _pad_cols(W, ctx.width).t(), precision=ctx.precision, gate=X if gate_dx else None)
+            if need_dX:  # the gate rides in the GEMM's store (a non-contiguous input gets a pass of its own)
+                fused_gate = gate_dx and X.is_contiguous()
+                dX = be.gemm(S, _pad_cols(W, ctx.width).t(), precision=ctx.precision, gate=X if fused_gate else None)
+                if gate_dx and not fused_gate:
+                    dX = be.relu_backward(dX, X)
         else:
             AX = saved[3]
             if need_dW:
@@ -381,8 +486,9 @@ class DistGCN(torch.nn.Module):
             w.uniform_(-s, s)  # same initialiser as src/graphcuda/python/gcn.py:43-45
             self.weights.append(torch.nn.Parameter(w))
 
-    def forward(self, X_local, graph, X_gathered=None, log_softmax: bool = True):
+    def forward(self, X_local, graph, X_gathered=None, log_softmax: bool = True, return_hidden: bool = False):
         h = X_local
+        hidden = [h]
         last = len(self.weights) - 1
         for i, W in enumerate(self.weights):
             fuse = 0
@@ -390,4 +496,6 @@ class DistGCN(torch.nn.Module):
                 fuse = (1 if i < last else 0) | (2 if i > 0 else 0)  # every layer but the last has a ReLU
             h = DistGCNConvFunction.apply(h, graph, W, i < last, None, self.precision,
                                           X_gathered if i == 0 else None, fuse)
-        return torch.log_softmax(h, dim=1) if log_softmax else h
+            hidden.append(h)
+        out = torch.log_softmax(h, dim=1) if log_softmax else h
+        return (out, hidden) if return_hidden else out

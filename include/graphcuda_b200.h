@@ -87,6 +87,12 @@ int gc_spmm_plan_build(const int32_t* rowptr, const int32_t* col, int64_t M, int
                        void* workspace, size_t workspace_bytes, void* stream);
 /* Scratch gc_spmm_csr_f32 needs with a plan of n_slots slots and F feature columns. */
 size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F);
+/* Synchronises `stream` and checks a built plan against the counts the caller
+ * holds: GC_OK, GC_ERR_INVALID when n_pieces / n_slots / n_cut are not the
+ * plan's own, GC_ERR_DEVICE_FLAG when an earlier gc_spmm_csr_f32 on this plan
+ * had to skip partial sums because its counts or scratch were too small
+ * (debug / test use: it reads the plan header back to the host). */
+int gc_spmm_plan_check(const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* stream);
 
 #define GC_EPI_RELU 1        /* out = max(out, 0) computed as out * (out > 0), reference gcn.cu:19-20 */
 #define GC_EPI_ACCUMULATE 2  /* out += result instead of out = result (bias/relu applied after the add) */
@@ -96,7 +102,12 @@ size_t gc_spmm_scratch_bytes(int64_t n_slots, int64_t F);
  * receives (pre-activation > 0) as 0.0f/1.0f with leading dimension ldY
  * (the fp32 mask of reference gcn.cu:19).  plan may be null: then every row is
  * one piece in natural order (n_pieces, n_cut ignored, no scratch needed).
- * With a plan, n_pieces and n_cut are the counts it was built with.
+ * With a plan, n_pieces, n_slots and n_cut are the counts it was built with;
+ * scratch_bytes must be at least gc_spmm_scratch_bytes(n_slots, F), else the
+ * call is refused with GC_ERR_WORKSPACE (nothing is launched, nothing truncated).
+ * Should the counts understate what the plan holds, the pieces that find no
+ * room are skipped and a sticky error word is raised in the plan header
+ * (read it back with gc_spmm_plan_check).
  * gate, when non-null, is a matrix of Y's shape and leading dimension: the
  * result is multiplied by (gate > 0) last of all -- the ReLU mask of the
  * PREVIOUS layer (reference gcn.cu:36) applied where this layer's input
@@ -108,9 +119,24 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
                     const float* H, int64_t ldH,
                     const float* bias, int epilogue,
                     float* Y, int64_t ldY, float* mask, const float* gate,
-                    const void* plan, int64_t n_pieces, int64_t n_cut,
+                    const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
                     void* scratch, size_t scratch_bytes,
                     void* stream);
+
+/*
+ * Measurement aid, no counterpart in the reference: the access pattern of the
+ * aggregation above with everything else removed.
+ *   Y[i, :] = sum over k < deg of H[idx[i * deg + k], :]      (i < n_rows)
+ * H is K x F (ldH), idx holds n_rows * deg row numbers in [0, K).  F, ldH, ldY
+ * multiples of 4, H and Y 16-byte aligned.  in_flight: 0 or 4 = four rows of H
+ * in flight per lane as the aggregation keeps, 8 = eight.  Timed on index
+ * lists of chosen locality it gives the rate at which gathered rows reach the
+ * SMs -- the practical ceiling of gc_spmm_csr_f32 when H is far larger than
+ * the L2 (bench.py reports it beside the HBM fraction).
+ */
+int gc_gather_sum_f32(const float* H, int64_t ldH, int64_t K, int64_t F,
+                      const int32_t* idx, int64_t n_rows, int64_t deg,
+                      float* Y, int64_t ldY, int in_flight, void* stream);
 
 /*
  * The same aggregation for callers that must not allocate device memory.

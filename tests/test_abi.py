@@ -43,7 +43,7 @@ def test_header_cites_the_reference():
 
 def test_status_strings_and_version():
     L = _lib.lib()
-    assert L.gc_abi_version() >= 2
+    assert L.gc_abi_version() >= 3
     assert L.gc_status_string(0) == b"ok"
     assert b"workspace" in L.gc_status_string(-4)
 
@@ -56,10 +56,17 @@ def test_argument_validation_without_gpu():
     # leading dimension too small
     assert L.gc_gemm_f32(0, 0, 8, 8, 8, 16, 4, 16, 8, 16, 8, None, 0, None, None, 0, None, 0, None) == -1
     # unknown epilogue bit
-    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, None, 0, 0, None, 0, None) == -1
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 4, 16, 4, None, 64, 16, 4, None, None, None, 0, 0, 0, None, 0, None) == -1
     # empty problems succeed without launching anything
     assert L.gc_gemm_f32(0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0, None, None, 0, None, 0, None) == 0
-    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, 0, None, 0, None) == 0
+    assert L.gc_spmm_csr_f32(None, None, None, 0, 0, 8, None, 8, None, 0, None, 8, None, None, None, 0, 0, 0, None, 0, None) == 0
+    # a plan that cuts rows needs gc_spmm_scratch_bytes(n_slots, F) of scratch: less is refused before any launch
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 8, 16, 8, None, 0, 16, 8, None, None, 16, 6, 3, 1, 16, 64, None) == -4
+    assert b"partial-sum rows" in L.gc_last_error()
+    # counts that cannot belong to one plan (a cut row has at least two pieces)
+    assert L.gc_spmm_csr_f32(16, 16, 16, 4, 4, 8, 16, 8, None, 0, 16, 8, None, None, 16, 6, 1, 1, 16, 4096, None) == -1
+    assert L.gc_gather_sum_f32(16, 6, 4, 6, 16, 4, 4, 16, 8, 0, None) == -1  # rows must be multiples of four floats
+    assert L.gc_gather_sum_f32(None, 8, 4, 8, None, 0, 4, None, 8, 0, None) == 0
     # evaluation tail and optimizer step: bad arguments are refused before any launch
     assert L.gc_argmax_accuracy_f32(16, 2, 4, 3, None, None, 0, None, None, None) == -1  # ld < C
     assert L.gc_argmax_accuracy_f32(16, 4, 4, 3, None, 16, 9, None, None, None) == -1  # more than 8 selections

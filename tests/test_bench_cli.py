@@ -29,6 +29,11 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert cb["kind"] in ("reference", "port") and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["gpu_launches"] == 0
+    # the arm runs without the package's CUDA library in the process
+    assert all("graphcuda_b200" not in so for so in d["shared_objects_of_this_repo_loaded"])
+    # the value is an extrapolation and says so: both measured points and the growth exponent are in the line
+    assert cb["extrapolated"] is True and cb["measured"]["ms_per_step"] > 0 and cb["second_point"]["ms_per_step"] > 0
+    assert 0.5 < cb["growth_exponent"] < 2.0
 
 
 def test_own_arm_needs_a_gpu_and_says_so():

@@ -90,3 +90,28 @@ def test_symmetry_verdict(cuda):
     assert as_adjacency(D.to(cuda)).symmetric
     D[3, 4] += 1.0
     assert not as_adjacency(D.to(cuda)).symmetric
+
+
+def test_degree_reordering_is_the_oracle_adjacency_of_the_relabelled_graph(cuda):
+    """reorder="degree": the CSR equals, bit for bit, what the oracle builds from the relabelled edge list;
+    the permutation is by decreasing degree (ties by old id) and products commute with it."""
+    from graphcuda_b200 import degree_order, normalized_adjacency, synth
+    n = 20000
+    e = synth.rmat_edges(15, n, 150_000, 7)
+    ei = synth.symmetrize(e)
+    adj = normalized_adjacency(ei.to(cuda), n, reorder="degree")
+    perm, inv = adj.perm.cpu(), adj.inv_perm.cpu()
+    deg = torch.bincount(ei[1], minlength=n)
+    assert torch.equal(perm, torch.argsort(deg, descending=True, stable=True))
+    assert torch.equal(inv[perm], torch.arange(n))
+    p2, i2 = degree_order(ei, n)  # the same helper on the CPU
+    assert torch.equal(p2, perm) and torch.equal(i2, inv)
+    _check_bit_exact(adj, O.normalized_adjacency_coo(inv[ei], n))
+    new_deg = (adj.rowptr[1:] - adj.rowptr[:-1]).cpu()
+    assert bool((new_deg[:-1] >= new_deg[1:]).all())  # heavy vertices first
+    # (P A P^T)(P H) = P (A H): aggregate in the new order, read the result back in the old one
+    plain = normalized_adjacency(ei.to(cuda), n)
+    H = torch.randn(n, 64, generator=torch.Generator().manual_seed(1)).to(cuda)
+    Y_old = plain.matmul(H)
+    Y_new = adj.matmul(H[adj.perm])
+    assert O.rel_fro(Y_new[adj.inv_perm], Y_old) < 1e-5

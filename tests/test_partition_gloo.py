@@ -63,6 +63,30 @@ def test_row_partition_bounds():
         RowPartition(10, 0)
 
 
+def test_nnz_balanced_partition():
+    """Block boundaries placed on the prefix sums of the row lengths: every block carries about nnz / world
+    non-zeros even when the rows are ordered by degree, and padded space round-trips."""
+    deg = torch.tensor([50, 30, 10, 4, 2, 1, 1, 1, 1, 0, 0, 0])
+    rowptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(deg, 0)]).to(torch.int32)
+    p = RowPartition(12, 3, rowptr=rowptr)
+    assert not p.uniform and p.starts[0] == 0 and p.starts[-1] == 12
+    sizes = [int(rowptr[b] - rowptr[a]) for a, b in zip(p.starts[:-1], p.starts[1:])]
+    assert sum(sizes) == 100 and max(sizes) <= 50  # no block holds more than the heaviest single row forces
+    assert p.block == max(b - a for a, b in zip(p.starts[:-1], p.starts[1:])) and p.padded == 3 * p.block
+    ids = torch.arange(12)
+    pos = p.to_padded(ids)
+    for r in range(3):
+        lo, hi = p.bounds(r)
+        assert torch.equal(pos[lo:hi], torch.arange(hi - lo) + r * p.block)
+        assert all(p.owner(i) == r for i in range(lo, hi))
+    full = torch.full((p.padded, 2), -1.0)
+    full[pos] = torch.arange(24.0).view(12, 2)
+    assert torch.equal(p.unpad(full), torch.arange(24.0).view(12, 2))
+    u = RowPartition(10, 4)
+    assert u.uniform and torch.equal(u.to_padded(ids[:10]), ids[:10])
+    assert torch.equal(u.unpad(torch.arange(24.0).view(12, 2)), torch.arange(20.0).view(10, 2))
+
+
 def _graph(n, seed):
     from graphcuda_b200 import synth
     e = synth.rmat_edges(max(4, (n - 1).bit_length()), n, n * 4, seed)
@@ -96,7 +120,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, n, dims, q, mode="rows", fuse=True):
+def _worker(rank, world, port, n, dims, q, mode="rows", fuse=True, balance="rows"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -108,7 +132,11 @@ def _worker(rank, world, port, n, dims, q, mode="rows", fuse=True):
         y = torch.randint(0, dims[-1], (n,), generator=g)
         be = TorchCPUBackend()
         if mode == "rows":
-            graph = PartitionedGraph(rowptr, col, val, n, backend=be)
+            graph = PartitionedGraph(rowptr, col, val, n, backend=be, balance=balance)
+        elif mode == "hybrid":
+            from graphcuda_b200.partition import HybridGraph
+            graph = HybridGraph(rowptr, col, val, be.make_adj(rowptr, col, val, (n, n)), n, backend=be,
+                                wide_from=10)
         else:
             graph = FeatureShardedGraph(be.make_adj(rowptr, col, val, (n, n)), n, backend=be)
         lo, hi = graph.lo, graph.hi
@@ -128,14 +156,17 @@ def _worker(rank, world, port, n, dims, q, mode="rows", fuse=True):
 
 
 @pytest.mark.parametrize("world,n,dims", [(2, 64, [12, 20, 20, 5]), (3, 50, [9, 16, 4]), (2, 33, [20, 8, 6])])
-@pytest.mark.parametrize("mode,fuse", [("rows", True), ("features", True), ("rows", False)])
+@pytest.mark.parametrize("mode,fuse", [("rows", True), ("features", True), ("rows", False), ("rows-nnz", True),
+                                       ("hybrid", True)])
 def test_partitioned_model_matches_single_process(world, n, dims, mode, fuse):
     """fuse: the ReLU backward of a hidden layer applied where the layer above produces its input gradient
     (in the GEMM's store, or in a pass after the aggregation's exchange), or as the reference places it."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode, fuse)) for r in range(world)]
+    balance = "nnz" if mode == "rows-nnz" else "rows"
+    mode = "rows" if mode == "rows-nnz" else mode
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode, fuse, balance)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]

@@ -184,3 +184,57 @@ def test_full_size_arxiv_like_graph(cuda):
     rs = adj.matmul(ones)[:, 0].cpu()
     ref_rs = torch.sparse.sum(A, dim=1).to_dense()
     assert O.rel_max(rs, ref_rs) < 1e-4
+
+
+def test_understated_scratch_is_refused_or_flagged_never_truncated_silently(cuda):
+    """C callers pass the plan's counts themselves.  Too little scratch for the slots they declare is refused
+    before any launch; slots they did not declare are skipped by the kernels and leave a sticky error word in
+    the plan that gc_spmm_plan_check reports.  Neither case writes outside the caller's buffers."""
+    from graphcuda_b200 import _lib
+    L = _lib.lib()
+    A = random_csr(400, 6000, 3.0, seed=21, long_rows=((2, 5000), (9, 3000)))
+    adj = to_gpu_csr(A, cuda)
+    F = 32
+    plan = adj.plan_for(F)
+    assert plan.n_cut >= 2 and plan.n_slots >= 4
+    H = torch.randn(6000, F, device=cuda)
+    Y = torch.zeros(400, F, device=cuda)
+    s = torch.cuda.current_stream().cuda_stream
+    need = L.gc_spmm_scratch_bytes(plan.n_slots, F)
+    scratch = torch.zeros(need, dtype=torch.uint8, device=cuda)
+
+    def call(n_slots, nbytes):
+        return L.gc_spmm_csr_f32(adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), 400, 6000, F,
+                                 H.data_ptr(), F, None, 0, Y.data_ptr(), F, None, None, plan.buf.data_ptr(),
+                                 plan.n_pieces, n_slots, plan.n_cut, scratch.data_ptr(), nbytes, s)
+
+    assert call(plan.n_slots, need - 16) == -4 and b"partial-sum rows" in L.gc_last_error()
+    assert L.gc_spmm_plan_check(plan.buf.data_ptr(), plan.n_pieces, plan.n_slots, plan.n_cut, s) == 0
+    # the right counts: the product, and the plan stays clean
+    assert call(plan.n_slots, need) == 0
+    assert O.rel_fro(Y, O.spmm(A, H.cpu())) < TOL
+    assert L.gc_spmm_plan_check(plan.buf.data_ptr(), plan.n_pieces, plan.n_slots, plan.n_cut, s) == 0
+    # counts that are not the plan's own are reported by the check ...
+    assert L.gc_spmm_plan_check(plan.buf.data_ptr(), plan.n_pieces, plan.n_slots - 1, plan.n_cut, s) == -1
+    # ... and a launch that understates the slots raises the sticky word instead of returning wrong sums unnoticed
+    assert call(plan.n_slots - 1, need) == 0
+    assert L.gc_spmm_plan_check(plan.buf.data_ptr(), plan.n_pieces, plan.n_slots, plan.n_cut, s) == -5
+    assert b"skipped" in L.gc_last_error()
+
+
+@pytest.mark.parametrize("F,deg,in_flight", [(256, 64, 4), (256, 7, 8), (100, 33, 4), (32, 64, 8), (8, 5, 4), (512, 3, 4)])
+def test_gather_sum_probe_is_a_real_sum(cuda, F, deg, in_flight):
+    """The measurement aid behind the gather ceiling computes what it says: Y[i] = sum_k H[idx[i, k]]."""
+    from graphcuda_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(F + deg)
+    K, n_rows = 5000, 777
+    H = torch.randn(K, F, generator=g)
+    idx = torch.randint(0, K, (n_rows, deg), generator=g, dtype=torch.int32)
+    ref = H[idx.long()].double().sum(1)
+    Hd, idxd = H.to(cuda), idx.to(cuda)
+    Y = torch.full((n_rows, F), float("nan"), device=cuda)
+    st = L.gc_gather_sum_f32(Hd.data_ptr(), F, K, F, idxd.data_ptr(), n_rows, deg, Y.data_ptr(), F, in_flight,
+                             torch.cuda.current_stream().cuda_stream)
+    assert st == 0, L.gc_last_error()
+    assert O.rel_fro(Y, ref) < 1e-5
