@@ -47,13 +47,16 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shrink", type=int, default=1,
                     help="divide nodes and edges by this factor (profiling captures and quick checks only)")
-    ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_simt", "tf32x3", "tf32"])
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_simt", "tf32x3", "tf32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary single-GPU measurements")
     ap.add_argument("--cpu-sample-div", type=int, default=32)
-    ap.add_argument("--partition", default="auto", choices=["auto", "features", "rows"],
-                    help="multi-GPU scheme: aggregation sharded over feature columns (all-to-all) or adjacency rows "
-                         "(all-gather); auto = rows up to 4 GPUs, features from 8 (measured cross-over)")
+    ap.add_argument("--partition", default="auto", choices=["auto", "features", "rows", "hybrid"],
+                    help="multi-GPU scheme: adjacency rows (all-gather of the aggregated matrix), feature columns "
+                         "(two transposes around the aggregation), or hybrid (rows for narrow and constant "
+                         "matrices, feature slabs for the hidden width); auto = rows up to 4 GPUs, hybrid from 8")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "collective"],
+                    help="auto: blocks move by peer copies through symmetric memory; collective: NCCL collectives")
     ap.add_argument("--no-parity", action="store_true",
                     help="skip the untimed CPU float64 check of the benchmarked graph's layers (profiler captures)")
     ap.add_argument("--profile-warmup", action="store_true",
@@ -154,6 +157,22 @@ class SpmmTimer:
             return out
 
         cls.matmul = timed
+        orig_blocks = cls.matmul_into_blocks
+
+        def timed_blocks(self_adj, H, *a, **kw):  # the aggregation whose stores go to the owners' buffers
+            if not timer.active:
+                return orig_blocks(self_adj, H, *a, **kw)
+            e_a = torch.cuda.Event(enable_timing=True)
+            e_b = torch.cuda.Event(enable_timing=True)
+            e_a.record()
+            out = orig_blocks(self_adj, H, *a, **kw)
+            e_b.record()
+            M, K = self_adj.shape
+            F = H.size(1)
+            timer.records.append((e_a, e_b, 4 * (M + 1) + 8 * self_adj.nnz + 4 * K * F + 4 * M * F, F, self_adj.nnz))
+            return out
+
+        cls.matmul_into_blocks = timed_blocks
 
     def summary(self):
         tot_ms, tot_b, gather_b = 0.0, 0, 0
@@ -168,6 +187,34 @@ class SpmmTimer:
             d[1] += nbytes
             d[2] += 1
         return tot_ms, tot_b, gather_b, per_f, len(self.records)
+
+
+def gather_ceiling(dev, n_rows_h: int, F: int = 256):
+    """Rate at which the memory system delivers gathered rows of an n_rows_h x F fp32 matrix to the SMs, measured
+    with gc_gather_sum_f32 (the aggregation's access pattern and nothing else) on three index lists: rows drawn
+    from a 64 MB region (every gather an L2 hit), from the whole matrix (every gather from DRAM) and a 73 % / 27 %
+    mix (the L2 hit rate ncu reports for the aggregation on this graph).  TB/s of gathered bytes."""
+    from graphcuda_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    H = torch.randn(n_rows_h, F, generator=g, device=dev)
+    n_out, deg = 1 << 19, 64
+    Y = torch.empty(n_out, F, device=dev)
+    hot = min((64 << 20) // (F * 4), n_rows_h)
+    cold = torch.randint(0, n_rows_h, (n_out * deg,), generator=g, device=dev, dtype=torch.int32)
+    warm = torch.randint(0, hot, (n_out * deg,), generator=g, device=dev, dtype=torch.int32)
+    mix = torch.where(torch.rand(n_out * deg, generator=g, device=dev) < 0.73, warm, cold)
+    res = {}
+    for name, idx in (("l2_resident", warm), ("l2_hit_73pct", mix), ("dram", cold)):
+        def run():
+            st = L.gc_gather_sum_f32(H.data_ptr(), F, n_rows_h, F, idx.data_ptr(), n_out, deg, Y.data_ptr(), F, 4,
+                                     torch.cuda.current_stream(dev).cuda_stream)
+            if st != 0:
+                raise RuntimeError(L.gc_last_error().decode())
+        ms = _time_ms(run, warm=2, iters=5)
+        res[name + "_TBs"] = n_out * deg * F * 4 / (ms * 1e-3) / 1e12
+    return res
 
 
 def measured_peaks():
@@ -326,6 +373,60 @@ def config_dict(cfg, args, world):
     }
 
 
+# ---------------------------------------------------------------- per-phase device times (one extra, untimed step)
+class PhaseProfile:
+    """CUDA-event pairs around every aggregation kernel call, GEMM call and exchange of ONE training step, with
+    each exchange waited for where it is issued (no overlap), so the phases add up: what a step spends in the
+    aggregation, the dense products, moving blocks between GPUs, and everything else."""
+
+    def __init__(self):
+        self.ev = {"spmm_ms": [], "gemm_ms": [], "exchange_ms": []}
+        self.undo = []
+
+    def _wrap(self, obj, name, phase, sync_work=False):
+        orig = getattr(obj, name)
+        prof = self
+
+        def timed(*a, **kw):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = orig(*a, **kw)
+            if sync_work and isinstance(out, tuple) and out[1] is not None:
+                out[1].wait()  # the gather is complete before the clock stops (and before anything overlaps it)
+            e1.record()
+            prof.ev[phase].append((e0, e1))
+            return out
+
+        setattr(obj, name, timed)
+        self.undo.append((obj, name, orig))
+
+    def install(self):
+        from graphcuda_b200 import partition as P
+        self._wrap(P.CudaBackend, "spmm", "spmm_ms")
+        self._wrap(P.CudaBackend, "spmm_into_blocks", "spmm_ms")  # the aggregation that stores into the owners
+        self._wrap(P.CudaBackend, "gemm", "gemm_ms")
+        self._wrap(P.PartitionedGraph, "all_gather_rows_async", "exchange_ms", sync_work=True)
+        self._wrap(P.FeatureShardedGraph, "rows_to_columns", "exchange_ms")
+        self._wrap(P.FeatureShardedGraph, "columns_to_rows", "exchange_ms")
+        self._wrap(P.PartitionedGraph, "all_reduce_sum", "exchange_ms")
+        self._wrap(P.FeatureShardedGraph, "all_reduce_sum", "exchange_ms")
+
+    def remove(self):
+        for obj, name, orig in reversed(self.undo):
+            setattr(obj, name, orig)
+        self.undo = []
+
+    def result(self, step_ms):
+        out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in self.ev.items()}
+        out["calls"] = {k: len(v) for k, v in self.ev.items()}
+        out["step_ms_serialised"] = step_ms
+        out["other_ms"] = step_ms - out["spmm_ms"] - out["gemm_ms"] - out["exchange_ms"]
+        big = max(("spmm_ms", "gemm_ms", "exchange_ms", "other_ms"), key=lambda k: out[k])
+        out["limiter"] = big[:-3]
+        return out
+
+
 # ---------------------------------------------------------------- parity (outside every timed region)
 PARITY_TOL = 1e-4
 
@@ -346,17 +447,22 @@ def _rel_errs(out, ref):
     return float(d.norm() / max(float(ref.norm()), 1e-300)), float(d.abs().max() / max(float(ref.abs().max()), 1e-300))
 
 
-def parity_block(model, X, y, graph, X_gathered, csr_host, n, world, rank, dev, gather_rows):
+def parity_block(make_model, X, y, graph, X_gathered, csr_host, n, world, rank, dev, gather_rows):
     """Compares the training path on the benchmarked graph with the reference's layer formulas evaluated on the
     CPU in float64 (src/graphcuda/cpp/gcn.cpp:10-15 forward, :34 weight gradient), layer by layer on the
     layer's own input as the GPU produced it:
       * forward: relu((A h_{l-1}) W_l) on ~1000 sampled rows (the highest- and lowest-degree rows, the rest
         drawn at random over ALL ranks' rows);
       * backward: the whole dW_1 = (A X)^T G_1 (a sum over every node, all-reduced over the ranks).
-    gather_rows(t) returns the full matrix (all ranks' row blocks) on every rank.  Runs once, untimed."""
+    gather_rows(t) returns the full matrix (all ranks' row blocks) on every rank.  Runs once, untimed.
+
+    The check runs on freshly initialised weights (the seed the benchmark starts from), not on the weights the
+    timed steps leave behind: with uniform random labels Adam drives this model to all-zero hidden activations
+    within a few steps (the loss settles at exactly ln 47), and a comparison of zeros with zeros would prove
+    nothing.  The logits of 64 fixed nodes from the same forward are returned as a probe that lines run on
+    different numbers of GPUs can be compared on."""
     import graphcuda_b200 as gc
-    for p_ in model.parameters():
-        p_.grad = None
+    model = make_model()
     if world == 1:
         out, hs = model(X, graph, log_softmax=False, return_hidden=True)
     else:
@@ -369,6 +475,12 @@ def parity_block(model, X, y, graph, X_gathered, csr_host, n, world, rank, dev, 
     full = [gather_rows(h.detach()) for h in hs]
     G1 = gather_rows((hs[1].grad * (hs[1].detach() > 0)).contiguous())  # gated gradient of layer 1 (idempotent)
     dW1 = list(model.parameters())[0].grad.detach().clone()
+    probe_rows = torch.linspace(0, n - 1, 64).long()
+    probe = full[-1][probe_rows.to(dev)].double()
+    logits_probe = {"rows": "64 nodes, torch.linspace(0, n-1, 64); weights as initialised from seed 0",
+                    "sum": float(probe.sum().item()), "abs_sum": float(probe.abs().sum().item()),
+                    "l2": float(probe.norm().item()),
+                    "first_row": [float(f"{float(v):.6e}") for v in probe[0].tolist()[:8]]}
     res = None
     if rank == 0:
         rowptr, col, val = csr_host
@@ -400,12 +512,11 @@ def parity_block(model, X, y, graph, X_gathered, csr_host, n, world, rank, dev, 
         res = {"ok": bool(worst < PARITY_TOL), "tolerance": PARITY_TOL, "max_rel_err": worst, "checks": layers,
                "reference": "CPU float64 evaluation of relu((A h) W) and (A X)^T G on the GPU's own layer inputs, "
                             "sampled rows over all ranks (forward) / all rows (weight gradient)",
-               "loss": float(loss.item())}
+               "weights": "freshly initialised (seed 0)", "loss_first_step": float(loss.item()),
+               "hidden_abs_mean": [float(f.abs().mean().item()) for f in full[1:]]}
     else:
         float(loss.item())
-    for p_ in model.parameters():
-        p_.grad = None
-    return res
+    return res, logits_probe
 
 
 # ---------------------------------------------------------------- our arm
@@ -415,13 +526,13 @@ def run_ours(args):
     import graphcuda_b200 as gc
     from graphcuda_b200 import _lib, adjacency, ops, synth
     from graphcuda_b200.models import GCN
-    from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, PartitionedGraph, RowPartition
+    from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, HybridGraph, PartitionedGraph
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.partition == "auto":
-        args.partition = "features" if world >= 8 else "rows"
+        args.partition = "hybrid" if world >= 8 else "rows"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local)
@@ -449,9 +560,11 @@ def run_ours(args):
         rows = n
     else:
         if args.partition == "rows":
-            part = PartitionedGraph(adj.rowptr, adj.col, adj.val, n, rank=rank, world=world)
+            part = PartitionedGraph(adj.rowptr, adj.col, adj.val, n, rank=rank, world=world, exchange=args.exchange)
+        elif args.partition == "hybrid":
+            part = HybridGraph(adj.rowptr, adj.col, adj.val, adj, n, rank=rank, world=world, exchange=args.exchange)
         else:
-            part = FeatureShardedGraph(adj, n, rank=rank, world=world)
+            part = FeatureShardedGraph(adj, n, rank=rank, world=world, exchange=args.exchange)
         lo, hi = part.lo, part.hi
         Xf = synth.normal_features(n, DIMS[0], seed=11, device=dev)
         yf = synth.uniform_labels(n, DIMS[-1], seed=12, device=dev)
@@ -535,27 +648,30 @@ def run_ours(args):
         src[:t.size(0)].copy_(t)
         full = torch.empty((B * world, t.size(1)), dtype=t.dtype, device=dev)
         dist.all_gather_into_tensor(full, src)
-        return full[:n]
+        return part.part.unpad(full)
 
-    probe_rows = torch.linspace(0, n - 1, 64).long()
-    with torch.no_grad():
-        logits = (model(X, adj, log_softmax=False) if world == 1
-                  else model(X, part, X_gathered=X_gathered, log_softmax=False))
-        lo_r = 0 if world == 1 else part.lo
-        mine = (probe_rows >= lo_r) & (probe_rows < lo_r + logits.size(0))
-        probe = torch.zeros((64, DIMS[-1]), dtype=torch.float32, device=dev)
-        probe[mine.to(dev)] = logits[(probe_rows[mine] - lo_r).to(dev)]
-        if world > 1:
-            dist.all_reduce(probe)
-        del logits
-    logits_probe = {"rows": "64 nodes, torch.linspace(0, n-1, 64)", "after_steps": n_warm + args.steps,
-                    "sum": float(probe.double().sum().item()), "abs_sum": float(probe.double().abs().sum().item()),
-                    "first_row": [round(float(v), 6) for v in probe[0].tolist()[:8]],
-                    "l2": float(probe.double().norm().item())}
-    parity = None
+    phases = None
+    if world > 1:  # rank 0's phases of one extra step, exchanges not overlapped
+        prof = PhaseProfile()
+        prof.install()
+        try:
+            barrier()
+            e0.record()
+            step(X, y, X_gathered)
+            e1.record()
+            barrier()
+            phases = prof.result(e0.elapsed_time(e1))
+        finally:
+            prof.remove()
+    parity = logits_probe = None
     if not args.no_parity:
-        parity = parity_block(model, X, y, adj if world == 1 else part, X_gathered, csr_host, n, world, rank, dev,
-                              gather_rows)
+        def fresh_model():
+            torch.manual_seed(0)
+            m = GCN(DIMS, precision=args.precision) if world == 1 else DistGCN(DIMS, precision=args.precision)
+            return m.to(dev)
+
+        parity, logits_probe = parity_block(fresh_model, X, y, adj if world == 1 else part, X_gathered, csr_host, n,
+                                            world, rank, dev, gather_rows)
         barrier()
 
     # ---- end to end: pinned host inputs copied in, loss read back, every step ----
@@ -609,12 +725,29 @@ def run_ours(args):
         "per_feature_width": {str(F): {"ms": d[0] / d[2], "gbs": d[1] / (d[0] * 1e-3) / 1e9, "launches": d[2]}
                               for F, d in sorted(per_f.items())},
         "share_of_step": sp_ms / args.steps / ms_step if ms_step > 0 else None,
-        # dram__bytes_read.sum + dram__bytes_write.sum of the F = 256 launch (pieces + finalize kernels), captured
-        # with ncu on the half-size graph and scaled by the non-zeros (profiles/spmm_pieces_kernel_rmat_products.md);
-        # the compulsory bytes of that launch are 6.04e9
+        # dram__bytes_read.sum + dram__bytes_write.sum of the F = 256 launch (pieces + finalize kernels) from an ncu
+        # capture on the half-size graph, scaled by the non-zeros: an offline figure, not a measurement of this
+        # run; the compulsory bytes of that launch are 6.04e9
         "traffic": 21.7e9 if (args.shrink == 1 and world == 1) else None,
+        "traffic_source": "profiled offline with ncu (dram__bytes_read.sum + dram__bytes_write.sum, F = 256 launch, "
+                          "pieces + finalize kernels) on the half-size graph, x2 for the non-zeros; the kernel "
+                          "source has not changed since that capture",
         "traffic_note": "bytes per F=256 launch at full size on 1 GPU; compulsory 6.04e9",
     }
+
+    if world == 1 and args.shrink == 1 and per_f.get(256):
+        # what the memory system can deliver for this access pattern, beside what the aggregation gets
+        try:
+            gc_ = gather_ceiling(dev, n, 256)
+            d256 = per_f[256]
+            gathered = adj.nnz * 256 * 4 / (d256[0] / d256[2] * 1e-3) / 1e12
+            gc_["aggregation_F256_gathered_TBs"] = gathered
+            gc_["aggregation_vs_l2_resident_ceiling"] = gathered / gc_["l2_resident_TBs"]
+            gc_["note"] = ("gathered bytes = nnz x F x 4; the aggregation's figure includes its L1 hits, the ceiling "
+                           "rows are uniform random (no L1 reuse)")
+            roofline["gather_ceiling"] = gc_
+        except Exception as ex:
+            roofline["gather_ceiling"] = {"error": repr(ex)[:200]}
 
     line = {
         "metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
@@ -628,13 +761,31 @@ def run_ours(args):
                 "value_without_prefetch": e2e_times[False]},
         "gpu_launches": int(launches), "clocks": clocks, "final_loss": final_loss, "setup_s": setup_s,
         "partition": (args.partition if world > 1 else "none"),
-        "parity": parity, "logits_probe": logits_probe,
+        "exchange": (("peer copies through symmetric memory" if part.symm is not None else "NCCL collectives")
+                     if world > 1 else "none"),
+        "parity": parity, "logits_probe": logits_probe, "phases": phases,
         "spmm_gbs": achieved, "spmm_pct_hbm_peak": 100.0 * achieved / peak,
     }
 
     if rank == 0 and world == 1 and not args.no_aux:
         try:
             line["aux"] = aux_measurements(dev, args)
+            # the same training step in the opt-in reduced-precision tiers (1e-2 relative): not the headline
+            for tier in ("tf32", "bf16"):
+                torch.manual_seed(0)
+                m2 = GCN(DIMS, precision=tier).to(dev)
+                o2 = gc.FusedAdam(m2.parameters(), lr=0.01)
+
+                def tier_step():
+                    o2.zero_grad(set_to_none=True)
+                    l2 = gc.log_softmax_nll_loss(m2(X, adj, log_softmax=False), y, scale=1.0 / n)
+                    l2.backward()
+                    o2.step()
+
+                line["aux"][f"rmat_products_train_step_ms_{tier}_tier"] = _time_ms(tier_step, warm=2, iters=5)
+                del m2, o2
+            torch.cuda.empty_cache()
+            line["aux"]["reference_cuda_same_box"] = reference_cuda_same_box(dev, adj)
             # the script's test(): no-grad forward of the same model + fused argmax / accuracy counts
             line["aux"]["rmat_products_eval_forward_argmax_ms"] = _time_ms(lambda: model.evaluate(X, adj, y), warm=2,
                                                                           iters=5)
@@ -719,6 +870,10 @@ def aux_measurements(dev, args):
             torch.cuda.synchronize()
             ts.append(a_.elapsed_time(b_))
         ms_cold = statistics.median(ts)
+        from graphcuda_b200 import ops as _ops
+        H16 = _ops.to_bf16(H)
+        ms16 = _time_ms(lambda: adj.matmul(H16, bias=b, relu=True))
+        out[f"arxiv_like_spmm_F{F}_bf16_gathers_ms"] = ms16
         out[f"arxiv_like_spmm_F{F}"] = {
             "ms_l2_warm": ms_warm, "ms_l2_flushed": ms_cold, "alg_bytes": nbytes,
             "gbs_l2_flushed": nbytes / (ms_cold * 1e-3) / 1e9, "frac_hbm_l2_flushed": nbytes / (ms_cold * 1e-3) / 1e9 / peak,
@@ -738,7 +893,7 @@ def aux_measurements(dev, args):
     W = synth.reference_init(128, 256, seed=4, device=dev)
     flops = 2.0 * c["nodes"] * 128 * 256
     gbytes = 4.0 * (c["nodes"] * 128 + 128 * 256 + c["nodes"] * 256)
-    for prec in ("tf32x3", "tf32", "fp32_simt"):
+    for prec in ("tf32x3", "tf32", "bf16", "fp32_simt"):
         ms = _time_ms(lambda: gc.gemm(Xa, W, precision=prec))
         out[f"arxiv_like_gemm_{prec}"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
                                           "gbs": gbytes / (ms * 1e-3) / 1e9, "frac_hbm": gbytes / (ms * 1e-3) / 1e9 / peak}
@@ -755,9 +910,10 @@ def aux_measurements(dev, args):
         fl = 2.0 * M * N * K
         by = 4.0 * (M * K + K * N + M * N)
         row = {}
-        for prec in ("tf32x3", "tf32"):
+        for prec in ("tf32x3", "tf32", "bf16"):
             ms = _time_ms(lambda: gc.gemm(A, B, precision=prec), warm=2, iters=5)
             row[prec] = {"ms": ms, "useful_tflops": fl / (ms * 1e-3) / 1e12, "gbs": by / (ms * 1e-3) / 1e9}
+        row["bf16"]["includes"] = "the conversion of both fp32 operands to bf16 inside the call"
         # same-box library context: cuBLAS SGEMM through torch.matmul (fp32, TF32 off), what the reference's
         # gemm_cublas wrapper calls (src/graphcuda/cuda/gemm_cublas.cu:37-48)
         torch.backends.cuda.matmul.allow_tf32 = False
@@ -781,17 +937,96 @@ def aux_measurements(dev, args):
     dadj = gc.DenseAdjacency(dense, symmetric=True)
     fl4 = 2.0 * n4 * 512 * 256 + 2.0 * n4 * n4 * 256
     row = {}
-    for prec in ("tf32x3", "tf32"):
+    peaks_tc = {}
+    try:
+        d_ = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks_tc = {"bf16": float(d_["bf16_tflops"])}
+    except Exception:
+        pass
+    for prec in ("tf32x3", "tf32", "bf16"):
         def fused():
             H = gc.gemm(X4, W4, precision=prec)
             return dadj.matmul(H, bias=b4, relu=True, precision=prec)
         ms = _time_ms(fused, warm=2, iters=5)
         row[prec] = {"ms": ms, "useful_tflops": fl4 / (ms * 1e-3) / 1e12,
-                     "adj_gbs": 4.0 * n4 * n4 / (ms * 1e-3) / 1e9}
+                     "adj_gbs": (2.0 if prec == "bf16" else 4.0) * n4 * n4 / (ms * 1e-3) / 1e9}
+        if prec == "bf16":
+            row[prec]["note"] = "the adjacency's bf16 copy (2.1 GB) is made once and reused; H is converted per call"
+            if "bf16" in peaks_tc:
+                row[prec]["frac_of_measured_bf16_peak"] = row[prec]["useful_tflops"] / peaks_tc["bf16"]
     # the same layer through the CSR path
     ms = _time_ms(lambda: a4.matmul(gc.gemm(X4, W4), bias=b4, relu=True), warm=2, iters=5)
     row["csr"] = {"ms": ms}
     out["dense_adj_32768_512_256"] = row
+    return out
+
+
+def reference_cuda_same_box(dev, full_graph=None):
+    """The reference's own CUDA extension (built unmodified for sm_100 by baseline/build_ref_cuda.py) timed on
+    this GPU beside this library on the same inputs: its library wrappers only -- spmm_cusparse (cuSPARSE COO
+    SpMM with a cudaMalloc / cudaFree per call, src/graphcuda/cuda/spmm_cusparse.cu:57-119), gemm_cublas
+    (gemm_cublas.cu:37-48) and the layer gcn_conv_forward / gcn_conv_backward (gcn.cu:5-52).  Its hand-written
+    matmul3 / matmul4 are not launched (they access out of bounds off 128-multiples: matmul3.cu:215-232,
+    matmul4.cu:185-201)."""
+    import graphcuda_b200 as gc
+    from graphcuda_b200 import synth
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import build_ref_cuda
+        ext = build_ref_cuda.load()
+    except Exception as ex:
+        return {"unavailable": f"reference CUDA extension not loadable here: {ex!r}"[:300]}
+    out = {"built_from": "src/graphcuda/cuda/*.cu, unmodified, -gencode arch=compute_100,code=sm_100"}
+
+    def layer_case(name, adj, X, W):
+        A = adj.to_sparse_coo()
+        n, fout = X.size(0), W.size(1)
+        dY = synth.normal_features(n, fout, seed=9, device=dev)
+        r = {}
+        Y, mask = ext.gcn_conv_forward(X, A, W, True)
+        ours = gc.GCNConv(W.size(0), fout).to(dev)
+        with torch.no_grad():
+            ours.weights.copy_(W)
+        Xg = X.clone().requires_grad_()
+        Yo = ours(Xg, adj)
+        r["forward_rel_diff_vs_reference"] = float((Yo - Y).norm() / Y.norm())
+        r["reference_spmm_cusparse_ms"] = _time_ms(lambda: ext.spmm_cusparse(A, X), warm=2, iters=5)
+        r["ours_spmm_ms"] = _time_ms(lambda: adj.matmul(X), warm=2, iters=5)
+        AX = adj.matmul(X)
+        r["reference_gemm_cublas_ms"] = _time_ms(lambda: ext.gemm_cublas(AX, W), warm=2, iters=5)
+        r["ours_gemm_ms"] = _time_ms(lambda: gc.gemm(AX, W), warm=2, iters=5)
+
+        def ref_layer():
+            Y_, m_ = ext.gcn_conv_forward(X, A, W, True)
+            ext.gcn_conv_backward(dY, X, A, W, True, m_)
+
+        def our_layer():
+            Xg.grad = None
+            ours.weights.grad = None
+            ours(Xg, adj).backward(dY)
+
+        r["reference_layer_fwd_bwd_ms"] = _time_ms(ref_layer, warm=2, iters=5)
+        r["ours_layer_fwd_bwd_ms"] = _time_ms(our_layer, warm=2, iters=5)
+        out[name] = r
+
+    try:
+        c = synth.CONFIGS["cora_like"]
+        e = synth.preferential_attachment_edges(c["nodes"], c["edges"], c["seed"]).to(dev)
+        adj = gc.normalized_adjacency(synth.symmetrize(e), c["nodes"], symmetric=True)
+        layer_case("cora_like_1433_16", adj, synth.bow_features(c["nodes"], c["features"], 0.0127, seed=1, device=dev),
+                   synth.reference_init(c["features"], c["hidden"], seed=4, device=dev))
+        c = synth.CONFIGS["rmat_arxiv"]
+        e = synth.rmat_edges(c["scale"], c["nodes"], c["edges"], c["seed"], device=dev)
+        adj = gc.normalized_adjacency(synth.symmetrize(e), c["nodes"], symmetric=True)
+        layer_case("arxiv_like_128_256", adj, synth.normal_features(c["nodes"], 128, seed=3, device=dev),
+                   synth.reference_init(128, 256, seed=4, device=dev))
+        del adj, e
+        if full_graph is not None:
+            n = full_graph.shape[0]
+            layer_case("products_like_100_256", full_graph, synth.normal_features(n, 100, seed=11, device=dev),
+                       synth.reference_init(100, 256, seed=4, device=dev))
+    except Exception as ex:
+        out["error"] = repr(ex)[:300]
     return out
 
 

@@ -36,12 +36,20 @@ SIGNATURES = {
     "gc_spmm_plan_check": (_int, [_void, _i64, _i64, _i64, _void]),
     "gc_spmm_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p, _i64,
                                _f32p, _f32p, _void, _i64, _i64, _i64, _void, _size, _void]),
+    "gc_spmm_csr_bf16h_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _void, _i64, _f32p, _int, _f32p, _i64,
+                                     _f32p, _f32p, _void, _i64, _i64, _i64, _void, _size, _void]),
+    "gc_spmm_csr_f32_blocks": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _void, _int,
+                                      _i64, _i64, _void, _i64, _i64, _i64, _void, _size, _void]),
     "gc_gather_sum_f32": (_int, [_f32p, _i64, _i64, _i64, _i32p, _i64, _i64, _f32p, _i64, _int, _void]),
     "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
                                        _i64, _f32p, _f32p, _void, _i64, _i64, _i64, _void]),
     "gc_gemm_workspace_bytes": (_size, [_int, _int, _i64, _i64, _i64, _int]),
     "gc_gemm_f32": (_int, [_int, _int, _i64, _i64, _i64, _f32p, _i64, _f32p, _i64, _f32p, _i64, _f32p, _int,
                            _f32p, _f32p, _int, _void, _size, _void]),
+    "gc_convert_f32_bf16": (_int, [_f32p, _i64, _i64, _i64, _void, _i64, _int, _void]),
+    "gc_gemm_bf16_workspace_bytes": (_size, [_i64, _i64, _i64]),
+    "gc_gemm_bf16_f32": (_int, [_i64, _i64, _i64, _void, _i64, _void, _i64, _f32p, _i64, _f32p, _int, _f32p, _f32p,
+                                _void, _size, _void]),
     "gc_gemm_resolve_precision": (_int, [_int, _int, _i64, _i64, _i64, _i64, _i64, _i64, _int]),
     "gc_gemm_check_flag": (_int, [_void, _void]),
     "gc_relu_backward_f32": (_int, [_f32p, _i64, _f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
@@ -67,6 +75,7 @@ SIGNATURES = {
 
 # epilogue / precision constants of the header
 SPMM_STATIC_SCRATCH_BYTES = 8 << 20
+SPMM_MAX_BLOCKS = 16
 EPI_RELU = 1
 EPI_ACCUMULATE = 2
 EPI_TRANSPOSED_OUT = 4
@@ -74,6 +83,7 @@ PREC_AUTO = -1
 PREC_FP32_SIMT = 0
 PREC_TF32X3 = 1
 PREC_TF32 = 2
+PREC_BF16 = 3
 
 _lib = None
 

@@ -115,12 +115,17 @@ class CSRAdjacency:
                out: Optional[torch.Tensor] = None, panel_cols: Optional[int] = None,
                gate: Optional[torch.Tensor] = None):
         """Y = A @ H (+bias)(ReLU).  Returns Y or (Y, mask).  gate (contiguous,
-        shape of Y): Y is multiplied by (gate > 0) in the store."""
+        shape of Y): Y is multiplied by (gate > 0) in the store.  H may be a bfloat16 matrix as ops.to_bf16 lays
+        it out (the reduced-precision tier: half the gathered bytes, fp32 sums and output)."""
         _require(H.dim() == 2, "B must be 2D")
         _require(H.size(0) == self.shape[1], "A.cols must match B.rows")
         _require(H.is_cuda and H.device == self.device, "A and B must be CUDA tensors on the same device")
-        _require(H.dtype == torch.float32, "B must be float32")
-        if H.stride(1) != 1 or (H.size(0) > 1 and H.stride(0) < H.size(1)):
+        h16 = H.dtype == torch.bfloat16
+        _require(H.dtype == torch.float32 or h16, "B must be float32 (or bfloat16 for the reduced-precision tier)")
+        if h16:
+            _require(H.stride(1) == 1 and H.size(1) % 8 == 0 and (H.size(0) <= 1 or H.stride(0) % 8 == 0)
+                     and H.data_ptr() % 16 == 0, "a bfloat16 B needs a width and row pitch that are multiples of 8")
+        elif H.stride(1) != 1 or (H.size(0) > 1 and H.stride(0) < H.size(1)):
             H = H.contiguous()
         M, K = self.shape
         F = H.size(1)
@@ -152,7 +157,8 @@ class CSRAdjacency:
             if plan is not None and plan.n_cut > 0:
                 scratch = arena.get("spmm", L.gc_spmm_scratch_bytes(plan.n_slots, F), dev)
             ldh = H.stride(0) if H.size(0) > 1 else max(F, 1)
-            st = L.gc_spmm_csr_f32(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
+            fn = L.gc_spmm_csr_bf16h_f32 if h16 else L.gc_spmm_csr_f32
+            st = fn(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
                                    H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None, epi,
                                    out.data_ptr(), ldy, mask.data_ptr() if mask is not None else None,
                                    gate.data_ptr() if gate is not None else None,
@@ -163,6 +169,53 @@ class CSRAdjacency:
                                    scratch.numel() if scratch is not None else 0, _stream(dev))
         _lib.check(st, "gc_spmm_csr_f32")
         return (out, mask) if want_mask else out
+
+    def matmul_into_blocks(self, H: torch.Tensor, blocks, block_rows: int, *, bias: Optional[torch.Tensor] = None,
+                           relu: bool = False, panel_cols: Optional[int] = None) -> None:
+        """A @ H (+bias)(ReLU) with row i stored in blocks[i // block_rows] at row i % block_rows.
+
+        blocks: float32 matrices of F columns, unit column stride and one common row stride; they may be views
+        of other GPUs' buffers (peer-mapped memory): the aggregation's stores then deliver every owner's rows
+        (gc_spmm_csr_f32_blocks).  The caller orders the use of those buffers across GPUs."""
+        import ctypes
+        _require(H.dim() == 2 and H.size(0) == self.shape[1] and H.is_cuda and H.device == self.device
+                 and H.dtype == torch.float32, "B must be a float32 CUDA matrix with A.cols rows")
+        if H.stride(1) != 1 or (H.size(0) > 1 and H.stride(0) < H.size(1)):
+            H = H.contiguous()
+        M, K = self.shape
+        F = H.size(1)
+        L = _lib.lib()
+        _require(1 <= len(blocks) <= _lib.SPMM_MAX_BLOCKS and len(blocks) * block_rows >= M,
+                 "blocks must cover the rows of A")
+        ld = blocks[0].stride(0)
+        for b in blocks:
+            _require(b.dtype == torch.float32 and b.dim() == 2 and b.size(1) == F and b.stride(1) == 1
+                     and b.stride(0) == ld and ld >= F, "blocks must be float32 [rows, F] views with one row stride")
+        for i, b in enumerate(blocks):
+            _require(b.size(0) >= min(block_rows, M - i * block_rows), "a block is shorter than its rows")
+        if bias is not None:
+            _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == F, "bias must be float32 [F]")
+            bias = bias.contiguous()
+        if M == 0 or F == 0:
+            return
+        ptrs = (ctypes.c_void_p * len(blocks))(*[b.data_ptr() for b in blocks])
+        dev = self.device
+        with torch.cuda.device(dev):
+            plan = self.plan_for(F, panel_cols) if self.use_plan else None
+            scratch = None
+            if plan is not None and plan.n_cut > 0:
+                scratch = arena.get("spmm", L.gc_spmm_scratch_bytes(plan.n_slots, F), dev)
+            ldh = H.stride(0) if H.size(0) > 1 else max(F, 1)
+            st = L.gc_spmm_csr_f32_blocks(self.rowptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr(), M, K, F,
+                                          H.data_ptr(), ldh, bias.data_ptr() if bias is not None else None,
+                                          EPI_RELU if relu else 0, ptrs, len(blocks), block_rows, ld,
+                                          plan.buf.data_ptr() if plan is not None else None,
+                                          plan.n_pieces if plan is not None else 0,
+                                          plan.n_slots if plan is not None else 0,
+                                          plan.n_cut if plan is not None else 0,
+                                          scratch.data_ptr() if scratch is not None else None,
+                                          scratch.numel() if scratch is not None else 0, _stream(dev))
+        _lib.check(st, "gc_spmm_csr_f32_blocks")
 
     def to_sparse_coo(self) -> torch.Tensor:
         counts = (self.rowptr[1:] - self.rowptr[:-1]).long()
@@ -200,8 +253,19 @@ class DenseAdjacency:
 
     def matmul(self, H: torch.Tensor, *, bias=None, relu=False, want_mask=False, accumulate_into=None, out=None,
                precision=None, gate=None):
-        from .ops import gemm
+        from .ops import gemm, gemm_bf16_operands, get_default_precision, to_bf16
         _require(accumulate_into is None, "accumulate is not available on the dense path")
+        if (precision or get_default_precision()) == "bf16" and not want_mask:
+            # the adjacency does not change between calls: its bf16 copy is made once (per version of the tensor)
+            # (remembered on the tensor itself, like the symmetry verdict, so that it lives exactly as long as A)
+            memo = getattr(self.A, "_gc_bf16", None)
+            if memo is None or memo[0] != self.A._version:
+                memo = (self.A._version, to_bf16(self.A))
+                try:
+                    self.A._gc_bf16 = memo
+                except Exception:
+                    pass
+            return gemm_bf16_operands(memo[1], to_bf16(H, transpose=True), bias=bias, relu=relu, out=out, gate=gate)
         return gemm(self.A, H, bias=bias, relu=relu, want_mask=want_mask, precision=precision, out=out, gate=gate)
 
 

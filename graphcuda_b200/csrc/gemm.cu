@@ -10,6 +10,10 @@ namespace {
 int resolve(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
             int precision) {
   if (precision == GC_PREC_FP32_SIMT) return GC_PREC_FP32_SIMT;
+  if (precision == GC_PREC_BF16) {  // operands are converted into the workspace: no alignment demands on the inputs
+    if (M <= 0 || N <= 0 || K <= 0) return gc::fail(GC_ERR_UNSUPPORTED, "bf16 GEMM needs non-empty sizes");
+    return GC_PREC_BF16;
+  }
   const bool tc_ok = gc::tc_supported(ta, tb, M, N, K, lda, ldb, ldc);
   if (precision == GC_PREC_TF32X3 || precision == GC_PREC_TF32) {
     if (!tc_ok)
@@ -46,6 +50,7 @@ size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int
     case GC_PREC_FP32_SIMT: return std::max<size_t>(simt, 256);
     case GC_PREC_TF32X3: return tc3;
     case GC_PREC_TF32: return tc1;
+    case GC_PREC_BF16: return gc::bf16_workspace_bytes(M, N, std::max<int64_t>(K, 1));
     default: return std::max(std::max(simt, tc3), size_t(256));
   }
 }
@@ -70,8 +75,40 @@ int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K, const f
   if (prec < 0) return prec;
   if (prec == GC_PREC_FP32_SIMT)
     return gc::gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, ep, workspace, workspace_bytes, st);
+  if (prec == GC_PREC_BF16)
+    return gc::gemm_bf16(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, ep, workspace, workspace_bytes, st);
   return gc::gemm_tc(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, ep, prec == GC_PREC_TF32X3 ? 3 : 1, workspace,
                      workspace_bytes, st);
+}
+
+int gc_convert_f32_bf16(const float* src, int64_t ld_src, int64_t rows, int64_t cols, uint16_t* dst, int64_t ld_dst,
+                        int transpose, void* stream) {
+  GC_REQUIRE(rows >= 0 && cols >= 0 && rows < INT32_MAX && cols < INT32_MAX, "gc_convert_f32_bf16: bad size");
+  if (rows == 0 || cols == 0) return GC_OK;
+  GC_REQUIRE(src && dst, "gc_convert_f32_bf16: null pointer");
+  GC_REQUIRE(ld_dst >= cols && ld_dst % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0,
+             "gc_convert_f32_bf16: ld_dst must be even and >= cols, dst 4-byte aligned");
+  GC_REQUIRE(ld_src >= (transpose ? rows : cols), "gc_convert_f32_bf16: ld_src too small");
+  return gc::convert_bf16(src, ld_src, rows, cols, dst, ld_dst, transpose != 0, gc::as_stream(stream));
+}
+
+size_t gc_gemm_bf16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 256;
+  return gc::bf16_core_workspace_bytes(M, N, K);
+}
+
+int gc_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t* A, int64_t lda, const uint16_t* Bt,
+                     int64_t ldb, float* C, int64_t ldc, const float* bias, int epilogue, float* mask,
+                     const float* gate, void* workspace, size_t workspace_bytes, void* stream) {
+  GC_REQUIRE(M >= 0 && N >= 0 && K >= 1, "gc_gemm_bf16_f32: bad size");
+  GC_REQUIRE(M < INT32_MAX && N < INT32_MAX && K < INT32_MAX, "gc_gemm_bf16_f32: size out of int32 range");
+  GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_TRANSPOSED_OUT)) == 0, "gc_gemm_bf16_f32: unknown epilogue bits");
+  if (M == 0 || N == 0) return GC_OK;
+  const bool tr = (epilogue & GC_EPI_TRANSPOSED_OUT) != 0;
+  GC_REQUIRE(A && Bt && C, "gc_gemm_bf16_f32: null pointer");
+  GC_REQUIRE(lda >= K && ldb >= K && ldc >= (tr ? M : N), "gc_gemm_bf16_f32: leading dimension too small");
+  gc::GemmEpilogue ep{bias, mask, gate, (epilogue & GC_EPI_RELU) ? 1 : 0, tr ? 1 : 0};
+  return gc::gemm_bf16_core(M, N, K, A, lda, Bt, ldb, C, ldc, ep, workspace, workspace_bytes, gc::as_stream(stream));
 }
 
 int gc_gemm_check_flag(const void* workspace, void* stream) {

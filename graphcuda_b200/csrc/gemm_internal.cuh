@@ -42,4 +42,16 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
             int64_t ldb, float* C, int64_t ldc, const GemmEpilogue& ep, int passes, void* workspace,
             size_t workspace_bytes, cudaStream_t st);
 
+// bf16 operands, fp32 accumulation (gemm_tcgen05.cu)
+size_t bf16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+size_t bf16_core_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int convert_bf16(const float* src, int64_t lds, int64_t rows, int64_t cols, uint16_t* dst, int64_t ldd, bool transpose,
+                 cudaStream_t st);
+int gemm_bf16_core(int64_t M, int64_t N, int64_t K, const uint16_t* A, int64_t lda, const uint16_t* Bt, int64_t ldb,
+                   float* C, int64_t ldc, const GemmEpilogue& ep, void* workspace, size_t workspace_bytes,
+                   cudaStream_t st);
+int gemm_bf16(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+              int64_t ldb, float* C, int64_t ldc, const GemmEpilogue& ep, void* workspace, size_t workspace_bytes,
+              cudaStream_t st);
+
 }  // namespace gc

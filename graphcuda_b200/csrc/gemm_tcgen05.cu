@@ -14,12 +14,13 @@
 // on the fly by four converter warps from the tile TMA just landed, so A is
 // read from HBM exactly once.
 //
-// CTA = 12 warps, persistent over 128 x BN output tiles:
-//   warp 0      TMA producer (one lane)           full[s]  <- bytes landed
-//   warp 1      MMA issuer (one lane)             empty[s] <- tcgen05.commit
-//   warp 2      TMEM allocator / idle
-//   warps 4-7   epilogue: tcgen05.ld -> bias/ReLU/mask -> global
-//   warps 8-11  converter: A tile -> A_lo tile    conv[s]
+// CTA = 16 warps, persistent over 128 x BN output tiles:
+//   warp 0        TMA producer (one lane)           full[s]  <- bytes landed
+//   warp 1        MMA issuer (one lane)             empty[s] <- tcgen05.commit
+//   warp 2        TMEM allocator / idle;  warp 3 idle
+//   warps 4-7     epilogue group 0: tcgen05.ld -> bias/ReLU/mask/gate -> global, even 32-column chunks
+//   warps 8-11    converter (three-pass mode): A tile -> A_lo tile (and B -> B_lo)    conv[s]
+//   warps 12-15   epilogue group 1: the odd 32-column chunks
 // Two TMEM accumulators (2 x BN columns) let the epilogue of tile i overlap
 // the main loop of tile i+1.
 //
@@ -104,6 +105,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f16 with bf16 operands (K = 16 per instruction: the same 32 bytes of every row as one kind::tf32 step)
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -164,6 +175,15 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn, bool a_mn, bool b_mn) 
          | (uint32_t(BM >> 4) << 24);   // M / 16
 }
 
+// Instruction descriptor for kind::f16 with bf16 operands (both K-major) and fp32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int bn) {
+  return (1u << 4)                     // D format: F32
+         | (1u << 7)                   // A format: BF16
+         | (1u << 10)                  // B format: BF16
+         | (uint32_t(bn >> 3) << 17)   // N / 8
+         | (uint32_t(BM >> 4) << 24);  // M / 16
+}
+
 struct TcParams {
   int M, N, K;
   float* C;
@@ -196,13 +216,17 @@ struct Cfg {
 // CONV_B: B_lo is produced in shared memory by the converter warps like A_lo
 // (large B operands: activations, gradients); otherwise it is loaded from a
 // pre-split copy (weights).
-template <int BN, int PASSES, bool A_MN, bool B_MN, bool CONV_B>
+// BF16: the operands are bf16 matrices (K-major, 64 elements = 128 bytes per row of a stage), one kind::f16
+// MMA per 32-byte step; everything else -- pipeline, TMEM, epilogue -- is the single-pass fp32 kernel.
+template <int BN, int PASSES, bool A_MN, bool B_MN, bool CONV_B, bool BF16 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapBlo, TcParams p) {
   using C_ = Cfg<BN, PASSES>;
   constexpr int S = C_::kStages;
   constexpr int BK = C_::BK;
+  constexpr int KE = BF16 ? 2 * BK : BK;  // K elements per stage (a stage row is BK * 4 bytes either way)
+  static_assert(!BF16 || (PASSES == 1 && !A_MN && !B_MN), "bf16 operands are K-major, one pass");
   constexpr bool kConvB = CONV_B && PASSES == 3;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -226,7 +250,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int nkb_total = (p.K + BK - 1) / BK;
+  const int nkb_total = (p.K + KE - 1) / KE;
   const int splits = p.splits > 1 ? p.splits : 1;
   const int kb_per = splits > 1 ? p.kb_per_split : nkb_total;
   // work item = (split, m tile, n tile), n fastest
@@ -280,14 +304,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             for (int c = 0; c < BM / 32; ++c)
               tma_load_2d(sA(s) + c * (BK * 128), &mapA, m0 + c * 32, kb * BK, bar_full(s));
           } else {
-            tma_load_2d(sA(s), &mapA, kb * BK, m0, bar_full(s));
+            tma_load_2d(sA(s), &mapA, kb * KE, m0, bar_full(s));
           }
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
               tma_load_2d(sB(s) + c * (BK * 128), &mapB, n0 + c * 32, kb * BK, bar_full(s));
           } else {
-            tma_load_2d(sB(s), &mapB, kb * BK, n0, bar_full(s));
+            tma_load_2d(sB(s), &mapB, kb * KE, n0, bar_full(s));
             if (PASSES == 3 && !kConvB) tma_load_2d(sBlo(s), &mapBlo, kb * BK, n0, bar_full(s));
           }
         }
@@ -307,7 +331,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+      constexpr uint32_t idesc = BF16 ? make_idesc_bf16(BN) : make_idesc(BN, A_MN, B_MN);
       constexpr uint32_t kMnLbo = BK * 128;  // bytes between 32-column chunks of an MN-major tile
       constexpr uint32_t kAStep = A_MN ? 1024u : uint32_t(UMMA_K * 4);  // start-address advance per k-step
       constexpr uint32_t kBStep = B_MN ? 1024u : uint32_t(UMMA_K * 4);
@@ -340,6 +364,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               umma_tf32(d_tmem, dal + aa, db + ab, idesc, acc);
               umma_tf32(d_tmem, da + aa, dbl + ab, idesc, 1u);
               umma_tf32(d_tmem, da + aa, db + ab, idesc, 1u);
+            } else if (BF16) {
+              umma_bf16(d_tmem, da + aa, db + ab, idesc, acc);
             } else {
               umma_tf32(d_tmem, da + aa, db + ab, idesc, acc);
             }
@@ -549,6 +575,45 @@ tc_splitk_reduce_kernel(int M, int N, int splits, const float* __restrict__ part
   }
 }
 
+// dst (bf16, R x Cc, pitch ldd) = src (fp32): as stored (transpose == 0: src is R x Cc) or transposed
+// (src is Cc x R).  Round to nearest even, as __float2bfloat16_rn does.
+__device__ __forceinline__ uint16_t to_bf16(float v) {
+  uint32_t u = __float_as_uint(v);
+  if ((u & 0x7F800000u) == 0x7F800000u) return uint16_t((u >> 16) | ((u & 0xFFFFu) ? 0x40u : 0u));  // inf / nan
+  return uint16_t((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+__global__ void __launch_bounds__(256)
+cvt_bf16_kernel(const float* __restrict__ src, int64_t lds, uint16_t* __restrict__ dst, int64_t ldd, int R, int Cc) {
+  // pairs of columns per thread; the pad columns [Cc, ldd) are zero-filled so that a K pitch rounded up to 8 holds zeros
+  const int64_t pairs_per_row = ldd / 2;
+  const int64_t total = int64_t(R) * pairs_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+    const int r = int(i / pairs_per_row), c = int(i % pairs_per_row) * 2;
+    const float a = c < Cc ? __ldg(src + int64_t(r) * lds + c) : 0.f;
+    const float b = c + 1 < Cc ? __ldg(src + int64_t(r) * lds + c + 1) : 0.f;
+    reinterpret_cast<uint32_t*>(dst + int64_t(r) * ldd)[c / 2] = uint32_t(to_bf16(a)) | (uint32_t(to_bf16(b)) << 16);
+  }
+}
+__global__ void __launch_bounds__(256)
+cvt_transpose_bf16_kernel(const float* __restrict__ in, int64_t ldin, uint16_t* __restrict__ out, int64_t ldout, int R,
+                          int Cc) {
+  // in is R x Cc (fp32), out is Cc x R (bf16, pitch ldout >= R, pad columns zero-filled), 32 x 32 tiles
+  __shared__ float t[32][33];
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int64_t tiles_r = (ldout + 31) / 32;  // cover the padded pitch so the pad is written
+  const int64_t tiles_c = (Cc + 31) / 32;
+  const int64_t tiles = tiles_r * tiles_c;
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int r0 = int(tile / tiles_c) * 32, c0 = int(tile % tiles_c) * 32;
+    for (int i = ty; i < 32; i += 8)
+      t[i][tx] = (r0 + i < R && c0 + tx < Cc) ? __ldg(in + int64_t(r0 + i) * ldin + c0 + tx) : 0.f;
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+      if (c0 + i < Cc && r0 + tx < ldout) out[int64_t(c0 + i) * ldout + r0 + tx] = to_bf16(t[tx][i]);
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------ host
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -590,7 +655,23 @@ int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int
   return GC_OK;
 }
 
+// Tensor map over a row-major bf16 matrix (rows x cols, pitch ld elements): box = 64 columns (128 bytes) x box_rows.
+int make_map_bf16(CUtensorMap* map, const uint16_t* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeFn enc = get_encode();
+  if (!enc) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  cuuint32_t box[2] = {64u, cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gc::fail(GC_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with CUresult %d", int(r));
+  return GC_OK;
+}
+
 inline int64_t round4(int64_t x) { return (x + 3) & ~int64_t(3); }
+inline int64_t round8(int64_t x) { return (x + 7) & ~int64_t(7); }
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 int pick_bn(int64_t N) {
@@ -792,6 +873,100 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
     rc = check_launch("gemm_tc split-K reduce");
   }
   return rc;
+}
+
+// ---- bf16 operands -------------------------------------------------------------------------------------------
+namespace {
+void bf16_splits(int64_t M, int64_t N, int64_t K, int bn, int& splits, int& kb_per_split) {
+  const int64_t tiles = ceil_div(M, BM) * ceil_div(N, bn);
+  const int64_t nkb = ceil_div(K, 64);
+  int64_t s = 1;
+  if (tiles * 2 <= kNumSMs && nkb >= 64) s = std::min<int64_t>(kNumSMs / tiles, nkb / 16);
+  s = std::max<int64_t>(1, s);
+  kb_per_split = int(ceil_div(nkb, s));
+  splits = int(ceil_div(nkb, kb_per_split));
+}
+}  // namespace
+
+size_t bf16_core_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  int splits, kbs;
+  bf16_splits(M, N, K, pick_bn(N), splits, kbs);
+  return 256 + (splits > 1 ? align256(size_t(splits) * size_t(M) * size_t(N) * 4) : 0);
+}
+
+size_t bf16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const size_t kp = size_t(round8(K));
+  return bf16_core_workspace_bytes(M, N, K) + align256(size_t(M) * kp * 2) + align256(size_t(N) * kp * 2);
+}
+
+int convert_bf16(const float* src, int64_t lds, int64_t rows, int64_t cols, uint16_t* dst, int64_t ldd, bool transpose,
+                 cudaStream_t st) {
+  // dst is rows x cols (pitch ldd, even); src is rows x cols, or cols x rows when transpose
+  const unsigned grid = kNumSMs * 8;
+  if (transpose) cvt_transpose_bf16_kernel<<<grid, 256, 0, st>>>(src, lds, dst, ldd, int(cols), int(rows));
+  else cvt_bf16_kernel<<<grid, 256, 0, st>>>(src, lds, dst, ldd, int(rows), int(cols));
+  return check_launch("convert to bf16");
+}
+
+// C = A * Bt^T with A (M x K) and Bt (N x K) bf16, K-major, pitches multiples of 8 elements, bases 16-byte aligned.
+int gemm_bf16_core(int64_t M, int64_t N, int64_t K, const uint16_t* A, int64_t lda, const uint16_t* Bt, int64_t ldb,
+                   float* C, int64_t ldc, const GemmEpilogue& ep, void* workspace, size_t workspace_bytes,
+                   cudaStream_t st) {
+  if (!workspace || workspace_bytes < bf16_core_workspace_bytes(M, N, K))
+    return fail(GC_ERR_WORKSPACE, "bf16 GEMM: workspace missing or too small");
+  if (!aligned16(workspace) || !aligned16(A) || !aligned16(Bt) || lda % 8 != 0 || ldb % 8 != 0)
+    return fail(GC_ERR_INVALID, "bf16 GEMM: operands and workspace must be 16-byte aligned, pitches multiples of 8");
+  char* ws = static_cast<char*>(workspace);
+  int* flag = reinterpret_cast<int*>(ws);
+  ws += 256;
+  const int bn = pick_bn(N);
+  TcParams p;
+  p.M = int(M); p.N = int(N); p.K = int(K);
+  p.C = C; p.ldc = ldc; p.ep = ep; p.flag = flag;
+  p.vec_store = (!ep.transposed && ldc % 4 == 0 && aligned16(C) && (!ep.mask || aligned16(ep.mask)) &&
+                 (!ep.gate || aligned16(ep.gate)) && (!ep.bias || aligned16(ep.bias))) ? 1 : 0;
+  bf16_splits(M, N, K, bn, p.splits, p.kb_per_split);
+  p.partial = p.splits > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+  CUtensorMap mA, mB;
+  int rc = make_map_bf16(&mA, A, M, K, lda, BM);
+  if (rc == GC_OK) rc = make_map_bf16(&mB, Bt, N, K, ldb, bn);
+  if (rc != GC_OK) return rc;
+  auto run = [&](auto kern, int smem, int bn_) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(GC_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const int64_t items = ceil_div(M, BM) * ceil_div(N, bn_) * (p.splits > 1 ? p.splits : 1);
+    kern<<<unsigned(std::min<int64_t>(items, kNumSMs)), kThreads, smem, st>>>(mA, mB, mB, p);
+    return check_launch("gemm_tf32_kernel (bf16 operands)");
+  };
+  if (bn == 64) rc = run(gemm_tf32_kernel<64, 1, false, false, false, true>, Cfg<64, 1>::kSmemBytes, 64);
+  else if (bn == 128) rc = run(gemm_tf32_kernel<128, 1, false, false, false, true>, Cfg<128, 1>::kSmemBytes, 128);
+  else rc = run(gemm_tf32_kernel<256, 1, false, false, false, true>, Cfg<256, 1>::kSmemBytes, 256);
+  if (rc != GC_OK) return rc;
+  if (p.splits > 1) {
+    const int64_t total = M * N;
+    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 256), kNumSMs * 8));
+    tc_splitk_reduce_kernel<<<g, 256, 0, st>>>(int(M), int(N), p.splits, p.partial, C, ldc, ep);
+    rc = check_launch("bf16 GEMM split-K reduce");
+  }
+  return rc;
+}
+
+// fp32 operands in any of the four layouts: both are converted (and re-laid K-major) into the workspace first.
+int gemm_bf16(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+              int64_t ldb, float* C, int64_t ldc, const GemmEpilogue& ep, void* workspace, size_t workspace_bytes,
+              cudaStream_t st) {
+  if (!workspace || workspace_bytes < bf16_workspace_bytes(M, N, K))
+    return fail(GC_ERR_WORKSPACE, "gemm_bf16: workspace missing or smaller than gc_gemm_workspace_bytes()");
+  if (!aligned16(workspace)) return fail(GC_ERR_INVALID, "gemm_bf16: workspace must be 16-byte aligned");
+  const int64_t kp = round8(K);
+  const size_t core = bf16_core_workspace_bytes(M, N, K);
+  char* ws = static_cast<char*>(workspace);
+  uint16_t* Ab = reinterpret_cast<uint16_t*>(ws + core);
+  uint16_t* Bb = reinterpret_cast<uint16_t*>(ws + core + align256(size_t(M) * kp * 2));
+  int rc = convert_bf16(A, lda, M, K, Ab, kp, ta, st);                // A given M x K, or K x M when ta
+  if (rc == GC_OK) rc = convert_bf16(B, ldb, N, K, Bb, kp, !tb, st);  // B given N x K when tb, else K x N
+  if (rc != GC_OK) return rc;
+  return gemm_bf16_core(M, N, K, Ab, kp, Bb, kp, C, ldc, ep, workspace, core, st);
 }
 
 }  // namespace gc

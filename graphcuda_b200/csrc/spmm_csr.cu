@@ -82,12 +82,33 @@ struct Epilogue {
   int accumulate;
 };
 
+// Output rows may be spread over several matrices of the same leading
+// dimension: row i lives in base[i / block_rows] at row i % block_rows.  That
+// is how a rank of the feature-sharded multi-GPU scheme stores its slab of the
+// product straight into every owner's buffer (peer-mapped memory, ordinary
+// stores): the aggregation's epilogue is the exchange.  block_rows == 0: one
+// matrix, the Y argument.
+struct RowBlocks {
+  float* base[GC_SPMM_MAX_BLOCKS];
+  int block_rows;
+};
+
+__device__ __forceinline__ float* out_row(const RowBlocks& rb, float* Y, int64_t ldY, int row) {
+  if (rb.block_rows == 0) return Y + int64_t(row) * ldY;
+  const int q = row / rb.block_rows;
+  return rb.base[q] + int64_t(row - q * rb.block_rows) * ldY;
+}
+
 template <int VW>
 struct Vec;
 template <>
 struct Vec<4> {
-  using T = float4;
+  using T = float4;   // accumulator / output vector
+  using HT = float;   // element type of H
+  using G = float4;   // one gathered vector of H
   static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ G gzero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ G gather(const HT* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
   static __device__ __forceinline__ T load(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
   static __device__ __forceinline__ T load_plain(const float* p) { return *reinterpret_cast<const float4*>(p); }
   static __device__ __forceinline__ T load_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
@@ -111,7 +132,11 @@ struct Vec<4> {
 template <>
 struct Vec<1> {
   using T = float;
+  using HT = float;
+  using G = float;
   static __device__ __forceinline__ T zero() { return 0.f; }
+  static __device__ __forceinline__ G gzero() { return 0.f; }
+  static __device__ __forceinline__ G gather(const HT* p) { return __ldg(p); }
   static __device__ __forceinline__ T load(const float* p) { return __ldg(p); }
   static __device__ __forceinline__ T load_plain(const float* p) { return *p; }
   static __device__ __forceinline__ T load_stream(const float* p) { return __ldcs(p); }
@@ -120,6 +145,44 @@ struct Vec<1> {
   static __device__ __forceinline__ T add(const T& a, const T& b) { return a + b; }
   static __device__ __forceinline__ T gt0(const T& a) { return a > 0.f ? 1.f : 0.f; }
   static __device__ __forceinline__ T mul(const T& a, const T& b) { return a * b; }
+};
+
+// H held in bf16 (the reduced-precision tier): a lane gathers 8 elements (16 bytes) at a time and accumulates
+// them in fp32; everything on the output side stays fp32.  Element 2i sits in the low half of word i.
+struct Float8 {
+  float4 a, b;
+};
+template <>
+struct Vec<8> {
+  using T = Float8;
+  using HT = uint16_t;
+  using G = uint4;
+  using V4 = Vec<4>;
+  static __device__ __forceinline__ T zero() { return Float8{V4::zero(), V4::zero()}; }
+  static __device__ __forceinline__ G gzero() { return make_uint4(0u, 0u, 0u, 0u); }
+  static __device__ __forceinline__ G gather(const HT* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ T load(const float* p) { return Float8{V4::load(p), V4::load(p + 4)}; }
+  static __device__ __forceinline__ T load_plain(const float* p) { return Float8{V4::load_plain(p), V4::load_plain(p + 4)}; }
+  static __device__ __forceinline__ T load_stream(const float* p) { return Float8{V4::load_stream(p), V4::load_stream(p + 4)}; }
+  static __device__ __forceinline__ void store(float* p, const T& v) {
+    V4::store(p, v.a);
+    V4::store(p + 4, v.b);
+  }
+  static __device__ __forceinline__ float lo(uint32_t u) { return __uint_as_float(u << 16); }
+  static __device__ __forceinline__ float hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+  static __device__ __forceinline__ void fma(T& acc, float s, const G& h) {
+    acc.a.x = fmaf(s, lo(h.x), acc.a.x);
+    acc.a.y = fmaf(s, hi(h.x), acc.a.y);
+    acc.a.z = fmaf(s, lo(h.y), acc.a.z);
+    acc.a.w = fmaf(s, hi(h.y), acc.a.w);
+    acc.b.x = fmaf(s, lo(h.z), acc.b.x);
+    acc.b.y = fmaf(s, hi(h.z), acc.b.y);
+    acc.b.z = fmaf(s, lo(h.w), acc.b.z);
+    acc.b.w = fmaf(s, hi(h.w), acc.b.w);
+  }
+  static __device__ __forceinline__ T add(const T& x, const T& y) { return Float8{V4::add(x.a, y.a), V4::add(x.b, y.b)}; }
+  static __device__ __forceinline__ T gt0(const T& x) { return Float8{V4::gt0(x.a), V4::gt0(x.b)}; }
+  static __device__ __forceinline__ T mul(const T& x, const T& y) { return Float8{V4::mul(x.a, y.a), V4::mul(x.b, y.b)}; }
 };
 
 // Applies accumulate / bias / mask / ReLU to one vector and stores it.
@@ -155,9 +218,9 @@ __global__ void __launch_bounds__(256, MIN_CTAS)
 spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict__ col,
                    const float* __restrict__ val, int n_pieces, const int32_t* __restrict__ p_start,
                    const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
-                   const float* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
+                   const typename Vec<VW>::HT* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
                    float* __restrict__ scratch, int64_t ldS, int slot_capacity, int32_t* __restrict__ overflow,
-                   Epilogue ep) {
+                   Epilogue ep, const __grid_constant__ RowBlocks rb) {
   using V = Vec<VW>;
   constexpr int PIECES_PER_CTA = 256 / GROUP;
   constexpr int PASS = GROUP * NACC * VW;
@@ -182,7 +245,7 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
     if (lane_g == 0) *overflow = 1;
     return;
   }
-  float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
+  float* yrow = direct ? out_row(rb, Y, ldY, target) : scratch + int64_t(~target) * ldS;
   float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
   const float* grow = (direct && ep.gate) ? ep.gate + int64_t(target) * ldY : nullptr;
   Epilogue my_ep = ep;
@@ -221,14 +284,14 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
           cj[u] = __shfl_sync(gmask, c, (j + u) % GROUP, GROUP);
           wj[u] = __shfl_sync(gmask, w, (j + u) % GROUP, GROUP);
         }
-        typename V::T h[U][NACC];
+        typename V::G h[U][NACC];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const float* hp = H + int64_t(cj[u]) * ldH + f0;
+          const typename V::HT* hp = H + int64_t(cj[u]) * ldH + f0;
           const bool valid = (j + u) < cnt;
 #pragma unroll
           for (int a = 0; a < NACC; ++a)
-            h[u][a] = (live[a] && valid) ? V::load(hp + (a * GROUP + lane_g) * VW) : V::zero();
+            h[u][a] = (live[a] && valid) ? V::gather(hp + (a * GROUP + lane_g) * VW) : V::gzero();
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -255,7 +318,7 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
                           const int32_t* __restrict__ p_len, const int32_t* __restrict__ p_target, int F,
                           const float* __restrict__ H, int64_t ldH, float* __restrict__ Y, int64_t ldY,
                           float* __restrict__ scratch, int64_t ldS, int slot_capacity,
-                          int32_t* __restrict__ overflow, Epilogue ep) {
+                          int32_t* __restrict__ overflow, Epilogue ep, const __grid_constant__ RowBlocks rb) {
   constexpr int G = 8;
   const int lane_g = threadIdx.x % G;
   const int v = blockIdx.x * (256 / G) + threadIdx.x / G;
@@ -315,7 +378,7 @@ spmm_pieces_narrow_kernel(const int32_t* __restrict__ rowptr, const int32_t* __r
       acc[a].w += __shfl_xor_sync(gmask, acc[a].w, o, G);
     }
   }
-  float* yrow = direct ? Y + int64_t(target) * ldY : scratch + int64_t(~target) * ldS;
+  float* yrow = direct ? out_row(rb, Y, ldY, target) : scratch + int64_t(~target) * ldS;
   float* mrow = (direct && ep.mask) ? ep.mask + int64_t(target) * ldY : nullptr;
   const float* grow = (direct && ep.gate) ? ep.gate + int64_t(target) * ldY : nullptr;
   Epilogue my_ep = ep;
@@ -334,7 +397,7 @@ __global__ void __launch_bounds__(256)
 spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, const int32_t* __restrict__ cut_slot0,
                      const int32_t* __restrict__ cut_nslots, const float* __restrict__ scratch, int64_t ldS,
                      int slot_capacity, int32_t* __restrict__ overflow, float* __restrict__ Y, int64_t ldY,
-                     Epilogue ep) {
+                     Epilogue ep, const __grid_constant__ RowBlocks rb) {
   using V = Vec<VW>;
   const int lane = threadIdx.x % 32;
   const int warps = gridDim.x * 8;
@@ -344,7 +407,7 @@ spmm_finalize_kernel(int F, int n_cut, const int32_t* __restrict__ cut_row, cons
     const int s_end = s0 + __ldg(cut_nslots + i);
     const int s1 = min(s_end, slot_capacity);
     if (s_end > slot_capacity && lane == 0) *overflow = 1;
-    float* yrow = Y + int64_t(row) * ldY;
+    float* yrow = out_row(rb, Y, ldY, row);
     float* mrow = ep.mask ? ep.mask + int64_t(row) * ldY : nullptr;
     const float* grow = ep.gate ? ep.gate + int64_t(row) * ldY : nullptr;
     for (int f = lane * VW; f < F; f += 32 * VW) {
@@ -555,27 +618,30 @@ int count_rows(const int32_t* rowptr, const int32_t* col, int M, int K, int pane
 // of up to 8 lanes: on a 2.3 M-non-zero graph they run F = 48..128 in
 // 0.11-0.13 ms against 0.15-0.22 ms at three; everything else is as fast or
 // faster at three (F = 512 on 126 M non-zeros: 17.9 against 20.5 ms).
-constexpr int pieces_min_ctas(int group, int nacc, int vw) { return (vw == 4 && nacc >= 3 && group <= 8) ? 2 : 3; }
+constexpr int pieces_min_ctas(int group, int nacc, int vw) {
+  return ((vw == 4 && nacc >= 3 && group <= 8) || (vw == 8 && nacc >= 2 && group <= 8)) ? 2 : 3;
+}
 
 template <int GROUP, int NACC, int VW, int U>
 void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
-                   const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
+                   const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const typename Vec<VW>::HT* H,
+                   int64_t ldH,
                    float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
-                   cudaStream_t st) {
+                   const RowBlocks& rb, cudaStream_t st) {
   constexpr int PER_CTA = 256 / GROUP;
   const unsigned grid = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
   constexpr int MINB = pieces_min_ctas(GROUP, NACC, VW);
   if (planned)
     spmm_pieces_kernel<GROUP, NACC, VW, U, true, MINB>
-        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep);
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep, rb);
   else
     spmm_pieces_kernel<GROUP, NACC, VW, U, false, MINB>
-        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep);
+        <<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep, rb);
 }
 
 #define GC_PIECES(G, A, VWID, UU)                                                                                 \
   launch_pieces<G, A, VWID, UU>(planned, rowptr, col, val, n_pieces, ps, pl, pt, F, H, ldH, Y, ldY, scratch, ldS, \
-                                cap, ovf, ep, st)
+                                cap, ovf, ep, rb, st)
 
 // GROUP x NACC 128-bit vectors cover a row of H; small groups keep several
 // pieces in flight per warp and four accumulators per lane amortise the
@@ -583,7 +649,7 @@ void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, cons
 void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                    const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
                    float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
-                   cudaStream_t st) {
+                   const RowBlocks& rb, cudaStream_t st) {
   const int units = F / 4;  // 128-bit vectors per row
   // Measured on the 126 M-non-zero graph: up to 8 floats the lane-per-non-zero kernel wins (F = 8: 0.99 ms
   // against 2.0 ms); from 12 to 32 floats groups of 4 lanes with one or two 128-bit vectors per lane and 4
@@ -595,10 +661,10 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
   do {                                                                                                          \
     if (planned)                                                                                                \
       spmm_pieces_narrow_kernel<NV, UU, true><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F, H, \
-                                                                   ldH, Y, ldY, scratch, ldS, cap, ovf, ep);    \
+                                                                   ldH, Y, ldY, scratch, ldS, cap, ovf, ep, rb);    \
     else                                                                                                        \
       spmm_pieces_narrow_kernel<NV, UU, false><<<grid, 256, 0, st>>>(rowptr, col, val, n_pieces, ps, pl, pt, F,  \
-                                                                    H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep); \
+                                                                    H, ldH, Y, ldY, scratch, ldS, cap, ovf, ep, rb); \
   } while (0)
     if (units <= 1) GC_NARROW(1, 4);
     else GC_NARROW(2, 4);
@@ -617,12 +683,25 @@ void dispatch_vec4(bool planned, const int32_t* rowptr, const int32_t* col, cons
 void dispatch_scalar(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
                      const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const float* H, int64_t ldH,
                      float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
-                     cudaStream_t st) {
+                     const RowBlocks& rb, cudaStream_t st) {
   if (F <= 8) GC_PIECES(8, 1, 1, 4);
   else if (F <= 16) GC_PIECES(16, 1, 1, 4);
   else if (F <= 32) GC_PIECES(32, 1, 1, 4);
   else if (F <= 64) GC_PIECES(32, 2, 1, 4);
   else GC_PIECES(32, 4, 1, 4);
+}
+// H in bf16: 8 elements per 16-byte vector; the same bytes in flight per lane as the fp32 mappings
+// (two accumulator vectors of 8 floats, up to 8 rows of H per round).
+void dispatch_bf16(bool planned, const int32_t* rowptr, const int32_t* col, const float* val, int n_pieces,
+                   const int32_t* ps, const int32_t* pl, const int32_t* pt, int F, const uint16_t* H, int64_t ldH,
+                   float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
+                   const RowBlocks& rb, cudaStream_t st) {
+  const int units = F / 8;
+  if (units <= 4) GC_PIECES(4, 1, 8, 4);
+  else if (units <= 8) GC_PIECES(4, 2, 8, 4);
+  else if (units <= 16) GC_PIECES(8, 2, 8, 8);
+  else if (units <= 32) GC_PIECES(16, 2, 8, 8);
+  else GC_PIECES(32, 2, 8, 4);
 }
 #undef GC_PIECES
 
@@ -754,23 +833,36 @@ int gc_spmm_plan_check(const void* plan, int64_t n_pieces, int64_t n_slots, int6
   return GC_OK;
 }
 
-int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
-                    const float* H, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
-                    float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
-                    void* scratch, size_t scratch_bytes, void* stream) {
+}  // extern "C"
+
+namespace {
+// The product behind gc_spmm_csr_f32 (rb.block_rows == 0, rows go to Y) and gc_spmm_csr_f32_blocks.
+// H16 non-null: H is read from that bf16 copy instead (H ignored).
+int spmm_run(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
+             const float* H, const uint16_t* H16, int64_t ldH, const float* bias, int epilogue, float* Y,
+             const RowBlocks& rb, int64_t ldY,
+             float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+             void* scratch, size_t scratch_bytes, void* stream) {
   GC_REQUIRE(M >= 0 && K >= 0 && F >= 0, "gc_spmm_csr_f32: negative size");
   GC_REQUIRE(M < INT32_MAX && K < INT32_MAX && F < INT32_MAX, "gc_spmm_csr_f32: size out of int32 range");
   GC_REQUIRE((epilogue & ~(GC_EPI_RELU | GC_EPI_ACCUMULATE)) == 0, "gc_spmm_csr_f32: unknown epilogue bits");
   if (M == 0 || F == 0) return GC_OK;
   GC_REQUIRE(rowptr && Y, "gc_spmm_csr_f32: null rowptr/Y");
   GC_REQUIRE(ldY >= F && (K == 0 || ldH >= F), "gc_spmm_csr_f32: leading dimension smaller than F");
-  GC_REQUIRE(K == 0 || H, "gc_spmm_csr_f32: null H");
+  GC_REQUIRE(K == 0 || H || H16, "gc_spmm_csr_f32: null H");
   cudaStream_t st = gc::as_stream(stream);
   Epilogue ep{bias, mask, gate, (epilogue & GC_EPI_RELU) ? 1 : 0, (epilogue & GC_EPI_ACCUMULATE) ? 1 : 0};
 
-  const bool vec4 = (F % 4 == 0) && (ldH % 4 == 0) && (ldY % 4 == 0) && gc::aligned16(H) && gc::aligned16(Y) &&
-                    (!bias || gc::aligned16(bias)) && (!mask || gc::aligned16(mask)) &&
-                    (!gate || gc::aligned16(gate));
+  bool blocks_aligned = true;
+  if (rb.block_rows)
+    for (int64_t b = 0; b * rb.block_rows < M; ++b) blocks_aligned = blocks_aligned && gc::aligned16(rb.base[b]);
+  const bool out_vec4 = (ldY % 4 == 0) && gc::aligned16(Y) && blocks_aligned && (!bias || gc::aligned16(bias)) &&
+                        (!mask || gc::aligned16(mask)) && (!gate || gc::aligned16(gate));
+  const bool vec4 = (F % 4 == 0) && (ldH % 4 == 0) && gc::aligned16(H) && out_vec4;
+  if (H16 && !((F % 8 == 0) && (ldH % 8 == 0) && gc::aligned16(H16) && out_vec4))
+    return gc::fail(GC_ERR_UNSUPPORTED,
+                    "gc_spmm_csr_bf16h_f32: F and ldH must be multiples of 8, H16 / Y / bias / mask / gate 16-byte "
+                    "aligned, ldY a multiple of 4");
   const bool planned = plan != nullptr;
   const int32_t *ps = nullptr, *pl = nullptr, *pt = nullptr;
   PlanView pv{};
@@ -800,23 +892,68 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
     }
   }
   float* sc = static_cast<float*>(scratch);
-  if (vec4)
-    dispatch_vec4(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, st);
+  if (H16)
+    dispatch_bf16(planned, rowptr, col, val, np, ps, pl, pt, int(F), H16, ldH, Y, ldY, sc, ldS, cap, ovf, ep, rb, st);
+  else if (vec4)
+    dispatch_vec4(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, rb, st);
   else
-    dispatch_scalar(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, st);
+    dispatch_scalar(planned, rowptr, col, val, np, ps, pl, pt, int(F), H, ldH, Y, ldY, sc, ldS, cap, ovf, ep, rb, st);
   int rc = gc::check_launch("gc_spmm_csr_f32 (pieces)");
   if (rc != GC_OK) return rc;
   if (planned && n_cut > 0) {
     const unsigned g = unsigned(std::min<int64_t>((n_cut + 7) / 8, gc::kNumSMs * 8));
-    if (vec4)
+    if (vec4 || H16)
       spmm_finalize_kernel<4><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
-                                                 cap, ovf, Y, ldY, ep);
+                                                 cap, ovf, Y, ldY, ep, rb);
     else
       spmm_finalize_kernel<1><<<g, 256, 0, st>>>(int(F), int(n_cut), pv.cut_row, pv.cut_slot0, pv.cut_nslots, sc, ldS,
-                                                 cap, ovf, Y, ldY, ep);
+                                                 cap, ovf, Y, ldY, ep, rb);
     rc = gc::check_launch("gc_spmm_csr_f32 (finalize)");
   }
   return rc;
+}
+}  // namespace
+
+extern "C" {
+
+int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
+                    const float* H, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
+                    float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                    void* scratch, size_t scratch_bytes, void* stream) {
+  RowBlocks rb{};
+  return spmm_run(rowptr, col, val, M, K, F, H, nullptr, ldH, bias, epilogue, Y, rb, ldY, mask, gate, plan, n_pieces,
+                  n_slots, n_cut, scratch, scratch_bytes, stream);
+}
+
+int gc_spmm_csr_bf16h_f32(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K, int64_t F,
+                          const uint16_t* H16, int64_t ldH, const float* bias, int epilogue, float* Y, int64_t ldY,
+                          float* mask, const float* gate, const void* plan, int64_t n_pieces, int64_t n_slots,
+                          int64_t n_cut, void* scratch, size_t scratch_bytes, void* stream) {
+  RowBlocks rb{};
+  GC_REQUIRE(K == 0 || M == 0 || F == 0 || H16, "gc_spmm_csr_bf16h_f32: null H16");
+  return spmm_run(rowptr, col, val, M, K, F, nullptr, H16, ldH, bias, epilogue, Y, rb, ldY, mask, gate, plan, n_pieces,
+                  n_slots, n_cut, scratch, scratch_bytes, stream);
+}
+
+int gc_spmm_csr_f32_blocks(const int32_t* rowptr, const int32_t* col, const float* val, int64_t M, int64_t K,
+                           int64_t F, const float* H, int64_t ldH, const float* bias, int epilogue,
+                           float* const* Y_blocks, int n_blocks, int64_t block_rows, int64_t ldY, const void* plan,
+                           int64_t n_pieces, int64_t n_slots, int64_t n_cut, void* scratch, size_t scratch_bytes,
+                           void* stream) {
+  GC_REQUIRE(n_blocks >= 1 && n_blocks <= GC_SPMM_MAX_BLOCKS, "gc_spmm_csr_f32_blocks: between 1 and %d blocks",
+             GC_SPMM_MAX_BLOCKS);
+  GC_REQUIRE(block_rows >= 1 && block_rows < INT32_MAX && M >= 0 && int64_t(n_blocks) * block_rows >= M,
+             "gc_spmm_csr_f32_blocks: n_blocks * block_rows must cover the M rows");
+  GC_REQUIRE((epilogue & ~GC_EPI_RELU) == 0, "gc_spmm_csr_f32_blocks: only bias and ReLU can be fused here");
+  GC_REQUIRE(Y_blocks, "gc_spmm_csr_f32_blocks: null block list");
+  RowBlocks rb{};
+  for (int b = 0; b < n_blocks; ++b) {
+    GC_REQUIRE(Y_blocks[b] || int64_t(b) * block_rows >= M, "gc_spmm_csr_f32_blocks: null block pointer");
+    rb.base[b] = Y_blocks[b];
+  }
+  rb.block_rows = int(block_rows);
+  return spmm_run(rowptr, col, val, M, K, F, H, nullptr, ldH, bias, epilogue, Y_blocks[0], rb, ldY, nullptr, nullptr,
+                  plan, n_pieces, n_slots, n_cut, scratch, scratch_bytes, stream);
 }
 
 // ---------------------------------------------------------------- no-allocation variant

@@ -58,6 +58,9 @@ def _adj_matmul(adj, H, precision, **kw):
     from .adjacency import DenseAdjacency
     if isinstance(adj, DenseAdjacency):
         return adj.matmul(H, precision=precision, **kw)
+    if (precision or ops.get_default_precision()) == "bf16" and H.size(1) % 8 == 0 and H.size(1) >= 8:
+        # reduced-precision tier: the aggregation gathers a bf16 copy of H (half the bytes), sums in fp32
+        return adj.matmul(ops.to_bf16(H), **kw)
     return adj.matmul(H, **kw)
 
 

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (EPI_ACCUMULATE, EPI_RELU, EPI_TRANSPOSED_OUT, PREC_AUTO, PREC_FP32_SIMT, PREC_TF32,
+from ._lib import (EPI_ACCUMULATE, EPI_RELU, EPI_TRANSPOSED_OUT, PREC_AUTO, PREC_BF16, PREC_FP32_SIMT, PREC_TF32,
                    PREC_TF32X3)
 
 PRECISIONS = {
@@ -23,6 +23,7 @@ PRECISIONS = {
     "fp32_simt": PREC_FP32_SIMT,  # IEEE fp32 FMA on CUDA cores, bit-stable
     "tf32x3": PREC_TF32X3,
     "tf32": PREC_TF32,          # opt-in, 1e-2 tolerance tier
+    "bf16": PREC_BF16,          # opt-in, 1e-2 tolerance tier: bf16 operands, fp32 accumulation
 }
 
 _default_precision = "fp32"
@@ -66,7 +67,12 @@ class _Arena:
             if buf is None or buf.numel() < nbytes:
                 # round up so growth is rare
                 size = max(256, int(nbytes * 1.25) + 255 & ~255)
-                buf = torch.zeros(size, dtype=torch.uint8, device=device)
+                new = torch.zeros(size, dtype=torch.uint8, device=device)
+                if buf is not None:
+                    # the first 256 bytes carry sticky state (the GEMM's error word): it moves with the buffer,
+                    # in stream order, so a flag raised before the growth is still there to be read afterwards
+                    new[:256].copy_(buf[:256])
+                buf = new
                 self._bufs[key] = buf
             return buf
 
@@ -162,6 +168,58 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     return (out, mask) if want_mask else out
 
 
+def to_bf16(X: torch.Tensor, *, transpose: bool = False) -> torch.Tensor:
+    """bf16 copy of a float32 matrix for the bf16 tier (round to nearest even), laid out for the tensor cores:
+    rows x cols with the row pitch rounded up to 8 elements and the pad zero-filled; ``transpose=True`` gives the
+    copy of X^T.  The result is a view [rows, cols] of the padded buffer."""
+    _require(X.dim() == 2 and X.is_cuda and X.dtype == torch.float32, "to_bf16: float32 CUDA matrix expected")
+    X = _row_major(X)
+    rows, cols = (X.size(1), X.size(0)) if transpose else (X.size(0), X.size(1))
+    ld = (cols + 7) // 8 * 8
+    out = torch.empty((rows, ld), dtype=torch.bfloat16, device=X.device)
+    with torch.cuda.device(X.device):
+        st = _lib.lib().gc_convert_f32_bf16(X.data_ptr(), _ld(X), rows, cols, out.data_ptr(), ld, 1 if transpose else 0,
+                                            _stream(X.device))
+    _lib.check(st, "gc_convert_f32_bf16")
+    return out[:, :cols]
+
+
+def gemm_bf16_operands(A16: torch.Tensor, Bt16: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+                       relu: bool = False, out: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
+    """C (float32) = A16 @ Bt16^T for operands already in bf16 (as to_bf16 lays them out: K contiguous, pitch a
+    multiple of 8).  What gemm(precision="bf16") runs after converting its operands; calling it directly lets a
+    constant operand (a dense adjacency, a weight) be converted once."""
+    _require(A16.dtype == torch.bfloat16 and Bt16.dtype == torch.bfloat16 and A16.is_cuda and Bt16.is_cuda,
+             "bf16 CUDA operands expected")
+    _require(A16.size(1) == Bt16.size(1), "A16 and Bt16 must share K")
+    _require(A16.stride(1) == 1 and Bt16.stride(1) == 1, "operands must have unit stride along K")
+    M, K = A16.shape
+    N = Bt16.size(0)
+    dev = A16.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=dev)
+        else:
+            _require(tuple(out.shape) == (M, N) and out.dtype == torch.float32 and out.is_contiguous(),
+                     "out has the wrong shape, dtype or layout")
+        if bias is not None:
+            _require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == N, "bias must be float32 [N]")
+            bias = bias.contiguous()
+        if gate is not None:
+            _require(gate.is_cuda and gate.dtype == torch.float32 and tuple(gate.shape) == (M, N)
+                     and gate.is_contiguous(), "gate must be a contiguous float32 tensor of the result's shape")
+        if M and N:
+            L = _lib.lib()
+            ws = arena.get("gemm", L.gc_gemm_bf16_workspace_bytes(M, N, K), dev)
+            st = L.gc_gemm_bf16_f32(M, N, K, A16.data_ptr(), A16.stride(0) if M > 1 else (K + 7) // 8 * 8,
+                                    Bt16.data_ptr(), Bt16.stride(0) if N > 1 else (K + 7) // 8 * 8, out.data_ptr(), N,
+                                    bias.data_ptr() if bias is not None else None, EPI_RELU if relu else 0, None,
+                                    gate.data_ptr() if gate is not None else None, ws.data_ptr(), ws.numel(),
+                                    _stream(dev))
+            _lib.check(st, "gc_gemm_bf16_f32")
+    return out
+
+
 def gemm_path(A: torch.Tensor, B: torch.Tensor, precision: Optional[str] = None) -> str:
     """Which back end gemm(A, B) takes: 'fp32_simt', 'tf32x3' or 'tf32'."""
     a, ta, lda = _as_operand(A)
@@ -170,7 +228,7 @@ def gemm_path(A: torch.Tensor, B: torch.Tensor, precision: Optional[str] = None)
     N = B.size(1)
     r = _lib.lib().gc_gemm_resolve_precision(ta, tb, M, N, K, lda, ldb, N, _prec(precision))
     _lib.check(min(r, 0), "gc_gemm_resolve_precision")
-    return {PREC_FP32_SIMT: "fp32_simt", PREC_TF32X3: "tf32x3", PREC_TF32: "tf32"}[r]
+    return {PREC_FP32_SIMT: "fp32_simt", PREC_TF32X3: "tf32x3", PREC_TF32: "tf32", PREC_BF16: "bf16"}[r]
 
 
 def check_gemm_flag(device: torch.device) -> None:

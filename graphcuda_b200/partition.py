@@ -21,6 +21,7 @@ on torch CPU ops under gloo.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -130,13 +131,113 @@ class CudaBackend:
     def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
         return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into, out=out)
 
-    def gemm(self, A, B, *, bias=None, relu=False, precision=None, gate=None):
+    def spmm_into_blocks(self, adj, H, blocks, block_rows, *, bias=None, relu=False):
+        """The aggregation with its rows stored into per-owner blocks (other GPUs' buffers)."""
+        adj.matmul_into_blocks(H, blocks, block_rows, bias=bias, relu=relu)
+
+    def gemm(self, A, B, *, bias=None, relu=False, precision=None, gate=None, out=None):
         from . import ops
-        return ops.gemm(A, B, bias=bias, relu=relu, precision=precision, gate=gate)
+        return ops.gemm(A, B, bias=bias, relu=relu, precision=precision, gate=gate, out=out)
 
     def relu_backward(self, dY, Y):
         from . import ops
         return ops.relu_backward(dY, Y)
+
+
+# ---------------------------------------------------------------- peer-memory exchange
+class SymmExchange:
+    """Exchange buffers in symmetric memory (every rank allocates the same
+    buffer; each rank can address every peer's copy over NVLink) and the
+    barriers that order their use.  CUDA + NCCL process groups only.
+
+    Data moves by plain peer copies -- a rank PULLS the blocks it needs from
+    the owners' buffers, or PUSHES slabs into the consumers' buffers -- issued
+    on side streams, so several copy engines / copy kernels run at once and
+    the compute stream keeps working.  Measured on two B200s, 1.25 GB per
+    rank: pulled all-gather 1.74 ms (721 GB/s in) against 2.68 ms for NCCL's
+    all_gather_into_tensor; no staging or pack / unpack copies are needed.
+    No multicast load is involved anywhere (ordinary loads and stores only).
+
+    Ordering.  Every exchange on a buffer runs
+        [local write] -> barrier -> peer copies -> (push only: barrier) -> use.
+    A rank may overwrite a buffer that peers read from (or that peers write
+    into) only after those peers have finished with its previous contents.
+    Their use is enqueued before their next barrier in stream order, so one
+    barrier of ANY later exchange proves it; only when the same buffer is used
+    by two exchanges in a row is an extra barrier issued first.
+    """
+
+    def __init__(self, group, device, world: int, rank: int):
+        import torch.distributed._symmetric_memory as symm
+        self._symm = symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = device
+        self.world, self.rank = world, rank
+        self._bufs = {}
+        self._seq = 0
+        self._last = {}
+        self._side = [torch.cuda.Stream(device=device) for _ in range(world)]
+
+    @staticmethod
+    def available(device) -> bool:
+        if os.environ.get("GRAPHCUDA_B200_NO_SYMM"):
+            return False
+        if not (isinstance(device, torch.device) and device.type == "cuda" and dist.is_initialized()):
+            return False
+        try:
+            import importlib
+            importlib.import_module("torch.distributed._symmetric_memory")
+            return dist.get_backend() == "nccl"
+        except Exception:
+            return False
+
+    def buffer(self, key, shape):
+        """(local tensor, handle, [every rank's tensor]) -- allocated and exchanged on first use, which every
+        rank must reach in the same order (it is a collective)."""
+        ent = self._bufs.get(key)
+        if ent is None:
+            t = self._symm.empty(tuple(shape), dtype=torch.float32, device=self.device)
+            t.zero_()
+            hdl = self._symm.rendezvous(t, self.group)
+            peers = [hdl.get_buffer(p, tuple(shape), torch.float32) for p in range(self.world)]
+            torch.cuda.current_stream(self.device).synchronize()
+            hdl.barrier(channel=0)  # nobody touches a peer's copy before it is zero-filled
+            ent = (t, hdl, peers)
+            self._bufs[key] = ent
+        return ent
+
+    def begin(self, key, hdl) -> None:
+        """Call before writing anything that peers read (or before writing into peers) for a new exchange."""
+        if self._last.get(key) == self._seq:  # the previous exchange used this very buffer: wait for its readers
+            hdl.barrier(channel=1)
+        self._seq += 1
+        self._last[key] = self._seq
+
+    def side_streams(self):
+        return self._side
+
+
+class _StreamJoin:
+    """What all_gather_rows_async returns in place of a collective's work handle: wait() makes the current
+    stream wait for the copies issued on the side streams."""
+
+    def __init__(self, streams):
+        self.streams = streams
+
+    def wait(self):
+        cur = torch.cuda.current_stream()
+        for st in self.streams:
+            cur.wait_stream(st)
+
+
+def _resolve_exchange(exchange, group, device, world, rank):
+    if isinstance(exchange, SymmExchange):
+        return exchange
+    if exchange in (None, "collective") or world == 1:
+        return None
+    if exchange != "auto":
+        raise ValueError("exchange must be 'auto', 'collective', None or a SymmExchange")
+    return SymmExchange(group, device, world, rank) if SymmExchange.available(device) else None
 
 
 # ---------------------------------------------------------------- partitioned graph
@@ -146,11 +247,14 @@ class PartitionedGraph:
 
     def __init__(self, rowptr, col, val, n_nodes: int, *, rank: Optional[int] = None,
                  world: Optional[int] = None, group=None, backend=None, rows_are_local: bool = False,
-                 balance: str = "rows", partition: Optional[RowPartition] = None):
+                 balance: str = "rows", partition: Optional[RowPartition] = None, exchange="auto"):
         """rowptr/col/val: the GLOBAL CSR (every rank passes the same), or with
         rows_are_local=True this rank's row block only (global column ids; pass
         the `partition` it was cut with).  balance: "rows" = equal row counts,
-        "nnz" = equal non-zeros per rank (needs the global rowptr)."""
+        "nnz" = equal non-zeros per rank (needs the global rowptr).
+        exchange: "auto" = peer-memory copies (SymmExchange) on CUDA + NCCL, the
+        process group's collectives otherwise; None / "collective" forces the
+        latter; or a SymmExchange to share with another graph object."""
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
@@ -180,8 +284,41 @@ class PartitionedGraph:
         self.device = val.device
         self._gather_bufs = {}
         self._stage_bufs = {}
+        self.symm = _resolve_exchange(exchange, self.group, self.device, self.world, self.rank)
 
     # -- collectives ----------------------------------------------------------
+    def out_slot(self, F: int, tag: str = "a"):
+        """Where a producer may write this rank's row block of a matrix that is about to be aggregated, so that
+        the exchange needs no staging copy (None when the exchange does not use peer memory)."""
+        if self.symm is None or self.world == 1:
+            return None
+        buf, _, _ = self.symm.buffer(("ag", F, tag), (self.part.padded, F))
+        return buf[self.rank * self.part.block: self.rank * self.part.block + self.rows]
+
+    def _pull_all_gather(self, H_local: torch.Tensor, tag: str):
+        F = H_local.size(1)
+        B = self.part.block
+        key = ("ag", F, tag)
+        buf, hdl, peers = self.symm.buffer(key, (self.part.padded, F))
+        self.symm.begin(key, hdl)
+        slot = buf[self.rank * B: self.rank * B + self.rows]
+        if H_local.data_ptr() != slot.data_ptr():
+            slot.copy_(H_local)
+        hdl.barrier(channel=0)  # every rank's block is in place
+        cur = torch.cuda.current_stream(self.device)
+        used = []
+        for k in range(1, self.world):
+            p = (self.rank + k) % self.world
+            lo_p, hi_p = self.part.bounds(p)
+            if hi_p == lo_p:
+                continue
+            st = self.symm.side_streams()[k]
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                buf[p * B: p * B + (hi_p - lo_p)].copy_(peers[p][p * B: p * B + (hi_p - lo_p)], non_blocking=True)
+            used.append(st)
+        return buf, _StreamJoin(used)
+
     def _gather_buffer(self, F: int, tag: str):
         key = (F, tag)
         buf = self._gather_bufs.get(key)
@@ -193,6 +330,8 @@ class PartitionedGraph:
     def all_gather_rows_async(self, H_local: torch.Tensor, tag: str = "a"):
         """Starts the all-gather of the row blocks; returns (gathered, work).
         `gathered` is indexable by global row id once work.wait() returned."""
+        if self.symm is not None and self.world > 1:
+            return self._pull_all_gather(H_local, tag)
         F = H_local.size(1)
         out = self._gather_buffer(F, tag)
         src = H_local
@@ -260,9 +399,10 @@ class FeatureShardedGraph:
     """
 
     def __init__(self, adj, n_nodes: int, *, rank: Optional[int] = None, world: Optional[int] = None, group=None,
-                 backend=None, device=None):
+                 backend=None, device=None, exchange="auto"):
         """adj: the whole adjacency as the backend's matrix object (CSRAdjacency
-        on CUDA), identical on every rank."""
+        on CUDA), identical on every rank.  exchange: as for PartitionedGraph
+        (peer-memory pushes instead of all_to_all_single + pack / unpack copies)."""
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
@@ -274,6 +414,7 @@ class FeatureShardedGraph:
         self.adj = adj
         self.device = device if device is not None else getattr(adj, "device", torch.device("cpu"))
         self._bufs = {}
+        self.symm = _resolve_exchange(exchange, self.group, self.device, self.world, self.rank)
 
     # -- helpers ----------------------------------------------------------------
     def slab_width(self, F: int) -> int:
@@ -306,6 +447,8 @@ class FeatureShardedGraph:
         P, B = self.world, self.part.block
         F = Y_rows.size(1)
         w = self.slab_width(F)
+        if self.symm is not None and P > 1:
+            return self._push_rows_to_columns(Y_rows, w, tag)
         send = self._buf(("s", w, tag), (P, B, w))
         if F == P * w and self.rows == B:
             send.copy_(Y_rows.reshape(B, P, w).permute(1, 0, 2))
@@ -321,11 +464,63 @@ class FeatureShardedGraph:
         """[P*B, slab] -> [rows_r, F]: the inverse transpose (a fresh tensor)."""
         P, B = self.world, self.part.block
         w = Z_cols.size(1)
+        if self.symm is not None and P > 1:
+            return self._push_columns_to_rows(Z_cols, F, tag)
         recv = self._buf(("r2", w, tag), (P, B, w))
         self._all_to_all(recv, Z_cols.view(P, B, w))
         out = recv.permute(1, 0, 2).reshape(B, P * w)[:self.rows, :F]
         # never hand out memory of the reusable receive buffer: the next exchange with this tag overwrites it
         return out.clone() if out.untyped_storage().data_ptr() == recv.untyped_storage().data_ptr() else out.contiguous()
+
+    # -- the same two transposes as pushes into the peers' buffers -------------------
+    def _push(self, pieces, hdl) -> None:
+        """pieces: (destination view in a peer's buffer, local source view); one side stream per peer."""
+        cur = torch.cuda.current_stream(self.device)
+        used = []
+        for k, (dst, src) in enumerate(pieces):
+            st = self.symm.side_streams()[k]
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                dst.copy_(src, non_blocking=True)
+            used.append(st)
+        for st in used:
+            cur.wait_stream(st)
+        hdl.barrier(channel=0)  # every peer's slabs have landed here, ours have landed there
+
+    def _push_rows_to_columns(self, Y_rows: torch.Tensor, w: int, tag: str) -> torch.Tensor:
+        """Rank r writes Y_r[:, slab q] straight into slot r of rank q's [P, B, w] buffer: no send buffer, no
+        pack copy.  Pad rows / columns of the buffers are zero from allocation and never written."""
+        P, B = self.world, self.part.block
+        F = Y_rows.size(1)
+        key = ("r2c", w, tag)
+        recv, hdl, peers = self.symm.buffer(key, (P, B, w))
+        self.symm.begin(key, hdl)
+        pieces = []
+        for k in range(P):
+            q = (self.rank + k) % P
+            c0, c1 = q * w, min((q + 1) * w, F)
+            if c1 > c0 and self.rows > 0:
+                pieces.append((peers[q][self.rank, :self.rows, :c1 - c0], Y_rows[:, c0:c1]))
+        self._push(pieces, hdl)
+        return recv.view(P * B, w)
+
+    def _push_columns_to_rows(self, Z_cols: torch.Tensor, F: int, tag: str) -> torch.Tensor:
+        """Rank r writes its slab of rank q's rows into columns [r w, (r+1) w) of rank q's [B, P w] buffer; the
+        result is a VIEW of that buffer, valid until the next exchange with the same width and tag."""
+        P, B = self.world, self.part.block
+        w = Z_cols.size(1)
+        key = ("c2r", w, tag)
+        out, hdl, peers = self.symm.buffer(key, (B, P * w))
+        self.symm.begin(key, hdl)
+        pieces = []
+        for k in range(P):
+            q = (self.rank + k) % P
+            lo_q, hi_q = self.part.bounds(q)
+            if hi_q > lo_q:
+                pieces.append((peers[q][:hi_q - lo_q, self.rank * w:(self.rank + 1) * w],
+                               Z_cols[q * B: q * B + (hi_q - lo_q)]))
+        self._push(pieces, hdl)
+        return out[:self.rows, :F]
 
     def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
         """Column slab of a matrix that does not change between steps (the input
@@ -344,9 +539,24 @@ class FeatureShardedGraph:
             bp = self._buf(("bias", w, tag), (self.world * w,))  # zero-filled once; the tail beyond F stays zero
             bp[:F].copy_(bias)
             b_slab = bp[self.rank * w:(self.rank + 1) * w]
+        if self.symm is not None and self.world > 1 and hasattr(self.backend, "spmm_into_blocks"):
+            return self._aggregate_into_owners(cols, F, w, b_slab, relu, tag)
         out = self._buf(("o", w, tag), (self.part.padded, w))
         self.backend.spmm(self.adj, cols[:self.n], bias=b_slab, relu=relu, out=out[:self.n])  # tail rows stay zero
         return self.columns_to_rows(out, F, tag)
+
+    def _aggregate_into_owners(self, cols, F: int, w: int, b_slab, relu: bool, tag: str) -> torch.Tensor:
+        """The aggregation kernel stores row i of this rank's slab straight into columns [r w, (r+1) w) of the
+        [B, P w] buffer of the rank that owns row i (peer memory): the columns -> rows transpose happens in the
+        kernel's epilogue, overlapped with its gathers, instead of in an exchange after it."""
+        P, B = self.world, self.part.block
+        key = ("c2r", w, tag)
+        out, hdl, peers = self.symm.buffer(key, (B, P * w))
+        self.symm.begin(key, hdl)
+        blocks = [peers[q][:, self.rank * w:(self.rank + 1) * w] for q in range(P)]
+        self.backend.spmm_into_blocks(self.adj, cols[:self.n], blocks, B, bias=b_slab, relu=relu)
+        hdl.barrier(channel=0)  # every rank's kernel has finished storing into this rank's buffer
+        return out[:self.rows, :F]
 
 
 class HybridGraph:
@@ -365,18 +575,23 @@ class HybridGraph:
     """
 
     def __init__(self, rowptr, col, val, adj, n_nodes: int, *, rank: Optional[int] = None,
-                 world: Optional[int] = None, group=None, backend=None, device=None, wide_from: int = 128):
+                 world: Optional[int] = None, group=None, backend=None, device=None, wide_from: int = 128,
+                 exchange="auto"):
         """rowptr/col/val: the global CSR (sliced into this rank's rows here);
         adj: the same matrix as the backend's object (every rank holds it whole)."""
         self.rows_graph = PartitionedGraph(rowptr, col, val, n_nodes, rank=rank, world=world, group=group,
-                                           backend=backend)
+                                           backend=backend, exchange=exchange)
+        # one exchange object for both: its barrier bookkeeping must see every exchange in order
         self.cols_graph = FeatureShardedGraph(adj, n_nodes, rank=rank, world=world, group=group, backend=backend,
-                                              device=device if device is not None else val.device)
+                                              device=device if device is not None else val.device,
+                                              exchange=self.rows_graph.symm if self.rows_graph.symm is not None
+                                              else "collective")
         g = self.rows_graph
         self.group, self.rank, self.world, self.part = g.group, g.rank, g.world, g.part
         self.lo, self.hi, self.rows, self.n = g.lo, g.hi, g.rows, g.n
         self.backend = g.backend
         self.device = g.device
+        self.symm = g.symm
         self.wide_from = int(wide_from)
 
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
@@ -384,6 +599,9 @@ class HybridGraph:
 
     def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
         return self.rows_graph.prepare_constant(X_local)
+
+    def out_slot(self, F: int, tag: str = "a"):
+        return self.rows_graph.out_slot(F, tag) if self.scheme_for(F, False) == "rows" else None
 
     def scheme_for(self, F: int, pre_gathered: bool) -> str:
         return "rows" if (pre_gathered or F < self.wide_from or self.world == 1) else "features"
@@ -394,14 +612,26 @@ class HybridGraph:
         return self.cols_graph.aggregate(H_local, bias=bias, relu=relu, tag=tag)
 
 
+def _gemm_into_slot(be, graph, A, B, precision, width: int, tag: str):
+    """A @ B written where the coming aggregation's exchange reads this rank's block from (no staging copy),
+    when the graph exchanges through peer memory; an ordinary product otherwise."""
+    slot_fn = getattr(graph, "out_slot", None)
+    slot = slot_fn(width, tag) if slot_fn is not None else None
+    if slot is None:
+        return be.gemm(A, B, precision=precision)
+    return be.gemm(A, B, precision=precision, out=slot)
+
+
 class DistGCNConvFunction(torch.autograd.Function):
     """One layer on the local row block; collectives inside forward/backward.
     The returned weight gradient is already summed over ranks."""
 
     @staticmethod
-    def forward(ctx, X, graph, W, apply_relu, bias, precision, X_gathered, fuse=0):
+    def forward(ctx, X, graph, W, apply_relu, bias, precision, X_gathered, fuse=0, layer=0):
         # fuse: bit 0 = the incoming gradient is already multiplied by this layer's ReLU mask;
         #       bit 1 = X is the ReLU output of the layer below: hand dX over multiplied by (X > 0)
+        # layer: index of the layer in its model; it names the exchange buffers, so that a result living in one
+        #        (peer-memory exchanges return views) is not overwritten by another layer of the same width
         be = graph.backend
         fin, fout = W.shape
         transform_first = fout < fin  # the partitioned adjacency is symmetric by contract
@@ -409,14 +639,14 @@ class DistGCNConvFunction(torch.autograd.Function):
         if transform_first:
             # odd output widths run zero-padded to a multiple of 4 (see engine._padded_width)
             width = _padded_width(graph.n, fin, fout)
-            H = be.gemm(X, _pad_cols(W, width), precision=precision)
+            H = _gemm_into_slot(be, graph, X, _pad_cols(W, width), precision, width, f"f{layer}")
             Y = graph.aggregate(H, bias=_pad_cols(bias, width) if bias is not None else None,
-                                relu=bool(apply_relu), tag="f")
+                                relu=bool(apply_relu), tag=f"f{layer}")
             if width != fout:
                 Y = Y[:, :fout]
             inter = None
         else:
-            AX = graph.aggregate(X, gathered=X_gathered, tag="f")
+            AX = graph.aggregate(X, gathered=X_gathered, tag=f"f{layer}")
             Y = be.gemm(AX, W, bias=bias, relu=bool(apply_relu), precision=precision)
             inter = AX
         ctx.graph = graph
@@ -427,6 +657,7 @@ class DistGCNConvFunction(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.has_inter = inter is not None
         ctx.fuse = int(fuse)
+        ctx.layer = int(layer)
         ctx.save_for_backward(*([X, W, Y] + ([inter] if inter is not None else [])))
         return Y
 
@@ -446,7 +677,7 @@ class DistGCNConvFunction(torch.autograd.Function):
             db = graph.all_reduce_sum(G.sum(0))
         if ctx.transform_first:
             fout = W.size(1)
-            S = graph.aggregate(_pad_cols(G, ctx.width), tag="b")  # A^T G = A G (symmetric)
+            S = graph.aggregate(_pad_cols(G, ctx.width), tag=f"b{ctx.layer}")  # A^T G = A G (symmetric)
             if need_dW:
                 dW = be.gemm(X.t(), S, precision=ctx.precision)[:, :fout].contiguous()
                 dW = graph.all_reduce_sum(dW)
@@ -460,11 +691,11 @@ class DistGCNConvFunction(torch.autograd.Function):
             if need_dW:
                 dW = graph.all_reduce_sum(be.gemm(AX.t(), G, precision=ctx.precision))
             if need_dX:
-                T = be.gemm(G, W.t(), precision=ctx.precision)
-                dX = graph.aggregate(T, tag="b")
+                T = _gemm_into_slot(be, graph, G, W.t(), ctx.precision, W.size(0), f"b{ctx.layer}")
+                dX = graph.aggregate(T, tag=f"b{ctx.layer}")
                 if gate_dx:  # the aggregation ends in an exchange or an accumulate: gate in a pass of its own
                     dX = be.relu_backward(dX, X)
-        return dX, None, dW, None, db, None, None, None
+        return dX, None, dW, None, db, None, None, None, None
 
 
 class DistGCN(torch.nn.Module):
@@ -495,7 +726,7 @@ class DistGCN(torch.nn.Module):
             if self.fuse_relu_backward:
                 fuse = (1 if i < last else 0) | (2 if i > 0 else 0)  # every layer but the last has a ReLU
             h = DistGCNConvFunction.apply(h, graph, W, i < last, None, self.precision,
-                                          X_gathered if i == 0 else None, fuse)
+                                          X_gathered if i == 0 else None, fuse, i)
             hidden.append(h)
         out = torch.log_softmax(h, dim=1) if log_softmax else h
         return (out, hidden) if return_hidden else out

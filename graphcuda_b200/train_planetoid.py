@@ -16,6 +16,8 @@ import time
 
 import torch
 
+from . import ops
+
 
 def main(argv=None) -> dict:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
@@ -84,6 +86,7 @@ def main(argv=None) -> dict:
             loss = train_eager()
         loss_value = loss.item()  # like the script's loss.item(): waits for the step
         dt = time.time() - t0
+        ops.check_gemm_flag(data.x.device)  # the step is complete: a tensor-core wait that ran out would show now
         total += dt
         accs = test()
         history.append(dict(epoch=epoch, time=dt, loss=loss_value, train=accs[0], val=accs[1], test=accs[2]))

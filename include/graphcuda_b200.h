@@ -124,6 +124,44 @@ int gc_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
                     void* stream);
 
 /*
+ * The same product with H held in bf16 (bit patterns, K x F, leading dimension ldH in elements; F and ldH
+ * multiples of 8, H16 16-byte aligned): the gathers move half the bytes, sums and the output stay fp32.
+ * Part of the opt-in reduced-precision tier (1e-2 relative), like GC_PREC_BF16 for the dense products; stands
+ * in for the same reference call (spmm_cusparse.cu:105-116).  gc_convert_f32_bf16 makes the copy.
+ */
+int gc_spmm_csr_bf16h_f32(const int32_t* rowptr, const int32_t* col, const float* val,
+                          int64_t M, int64_t K, int64_t F,
+                          const uint16_t* H16, int64_t ldH,
+                          const float* bias, int epilogue,
+                          float* Y, int64_t ldY, float* mask, const float* gate,
+                          const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                          void* scratch, size_t scratch_bytes,
+                          void* stream);
+
+/*
+ * The same product with its rows spread over several output matrices: row i is
+ * written to Y_blocks[i / block_rows] at row i % block_rows (leading dimension
+ * ldY in all of them).  Y_blocks is a HOST array of n_blocks (<= GC_SPMM_MAX_BLOCKS)
+ * device pointers, read during the call.  No counterpart in the reference
+ * (it is single-GPU): in the feature-sharded multi-GPU scheme every rank
+ * aggregates a slab of columns for ALL nodes and the rows belong to different
+ * ranks, so the blocks are the owners' buffers, peer-mapped over NVLink, and the
+ * aggregation's own stores deliver the result -- the exchange that would follow
+ * the kernel happens inside it (ordinary stores; the caller orders the use of
+ * the buffers with its own cross-GPU barrier).  Only bias and ReLU can be
+ * fused here (mask, gate and accumulate read or write matrices of Y's shape).
+ */
+#define GC_SPMM_MAX_BLOCKS 16
+int gc_spmm_csr_f32_blocks(const int32_t* rowptr, const int32_t* col, const float* val,
+                           int64_t M, int64_t K, int64_t F,
+                           const float* H, int64_t ldH,
+                           const float* bias, int epilogue,
+                           float* const* Y_blocks, int n_blocks, int64_t block_rows, int64_t ldY,
+                           const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                           void* scratch, size_t scratch_bytes,
+                           void* stream);
+
+/*
  * Measurement aid, no counterpart in the reference: the access pattern of the
  * aggregation above with everything else removed.
  *   Y[i, :] = sum over k < deg of H[idx[i * deg + k], :]      (i < n_rows)
@@ -191,6 +229,8 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
 #define GC_PREC_FP32_SIMT 0    /* IEEE fp32 FMA on CUDA cores, fixed summation order */
 #define GC_PREC_TF32X3 1       /* tcgen05 kind::tf32, split operands, three MMA passes, fp32 accumulate in TMEM */
 #define GC_PREC_TF32 2         /* tcgen05 kind::tf32, one pass (opt-in, 1e-2 tolerance tier) */
+#define GC_PREC_BF16 3         /* tcgen05 kind::f16 on bf16 copies of both operands made in the workspace, fp32
+                                  accumulate (opt-in, 1e-2 tolerance tier; twice the TF32 tensor rate) */
 
 #define GC_EPI_TRANSPOSED_OUT 4 /* store C transposed: C is N x M with leading dimension ldc (mask likewise) */
 
@@ -205,6 +245,25 @@ int gc_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K,
  * (never AUTO), or a negative error. */
 int gc_gemm_resolve_precision(int transA, int transB, int64_t M, int64_t N, int64_t K,
                               int64_t lda, int64_t ldb, int64_t ldc, int precision);
+/*
+ * The bf16 tier with operands the caller keeps in bf16 (a constant matrix -- a dense adjacency, weights --
+ * is converted once instead of on every call).  Same role as above: cublasSgemm at
+ * src/graphcuda/cuda/gemm_cublas.cu:37-48 and the dense adjm.mm(X) of src/graphcuda/cpp/gcn.cpp:10,
+ * under the 1e-2 tolerance tier.
+ * gc_convert_f32_bf16: dst (bf16 bit patterns, rows x cols, pitch ld_dst) = src rounded to nearest even; src is
+ *   rows x cols (transpose = 0) or cols x rows (transpose = 1); columns [cols, ld_dst) of dst are zero-filled.
+ * gc_gemm_bf16_f32: C[M,N] (fp32) = A[M,K] * Bt[N,K]^T, both operands bf16 with K contiguous, pitches multiples
+ *   of 8 elements, bases 16-byte aligned; fp32 accumulation; epilogue arguments as gc_gemm_f32.
+ */
+int gc_convert_f32_bf16(const float* src, int64_t ld_src, int64_t rows, int64_t cols,
+                        uint16_t* dst, int64_t ld_dst, int transpose, void* stream);
+size_t gc_gemm_bf16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int gc_gemm_bf16_f32(int64_t M, int64_t N, int64_t K,
+                     const uint16_t* A, int64_t lda, const uint16_t* Bt, int64_t ldb,
+                     float* C, int64_t ldc,
+                     const float* bias, int epilogue, float* mask, const float* gate,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* Tensor-core kernels bound every wait; a wait that ran out sets a flag word
  * at the start of the workspace.  Synchronises `stream`, reads it back and
  * returns GC_OK or GC_ERR_DEVICE_FLAG (debug / test use). */

@@ -122,7 +122,7 @@ GEMM_SHAPES = [(4096, 4096, 4096), (8192, 8192, 8192), (1 << 20, 64, 128), (1 <<
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL), ("tf32", TOL_LOW)])
+@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL), ("tf32", TOL_LOW), ("bf16", TOL_LOW)])
 def test_operator_gemm_at_the_timed_sizes(cuda, M, N, K, prec, tol):
     import graphcuda_b200 as gc
     from graphcuda_b200 import ops
@@ -162,7 +162,7 @@ def test_matmul_names_at_a_timed_size(cuda):
 
 
 # ---------------------------------------------------------------- dense adjacency, N = 32,768
-@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL), ("tf32", TOL_LOW)])
+@pytest.mark.parametrize("prec,tol", [("tf32x3", TOL), ("tf32", TOL_LOW), ("bf16", TOL_LOW)])
 def test_dense_adjacency_layer_at_32768(cuda, prec, tol):
     import graphcuda_b200 as gc
     from graphcuda_b200 import ops, synth

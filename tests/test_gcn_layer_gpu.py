@@ -215,7 +215,8 @@ def test_cora_like_training_logits_and_argmax(cuda, kind):
 
 def test_bias_relu_layer_arxiv_like_shape(cuda):
     """Single layer with bias + ReLU on a reduced R-MAT graph, 128 -> 256 (the
-    tensor-core path): relu((A X) W + b) against the oracle, fp32 and TF32."""
+    tensor-core path): relu((A X) W + b) against the oracle, fp32 and the two
+    reduced-precision tiers (single-pass TF32, bf16) at 1e-2."""
     import graphcuda
     from graphcuda_b200 import synth
     n = 20_000
@@ -235,7 +236,8 @@ def test_bias_relu_layer_arxiv_like_shape(cuda):
     pre = A.mm(Xr).mm(Wr) + br
     Yr = pre * (pre > 0)
     # one reference gradient per tolerance tier: ties are excluded at the tier's own resolution
-    for prec, tol in ((None, TOL), ("tf32", TOL_TF32)):
+    # "bf16": bf16 operands in the dense products and a bf16 copy of the matrix being aggregated, fp32 sums
+    for prec, tol in ((None, TOL), ("tf32", TOL_TF32), ("bf16", TOL_TF32)):
         for t in (Xr, Wr, br):
             t.grad = None
         dYt = untie(dY, pre.detach(), rel=tol)

@@ -194,3 +194,77 @@ def test_square_sweep(cuda, S):
     A, B = _rand(S, S, S), _rand(S, S, S + 1)
     ref = O.matmul(A, B)
     assert O.rel_fro(graphcuda.gemm_cublas(A.to(cuda), B.to(cuda)), ref) < TOL_FP32
+
+
+# ---------------------------------------------------------------- bf16 tier (opt-in, 1e-2)
+TOL_BF16 = 1e-2
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES + [(300, 200, 7), (1, 1, 1), (2048, 2048, 2048)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_bf16_tier_all_layouts(cuda, shape, ta, tb):
+    """precision="bf16": both operands are converted to bf16 (round to nearest even) into the workspace, in any of
+    the four storage layouts and with odd sizes / pitches, then multiplied with kind::f16 MMAs and fp32
+    accumulation.  Reference: the same product in float64; tolerance of the reduced-precision tier."""
+    from graphcuda_b200 import gemm, ops
+    M, N, K = shape
+    A, B = _rand(M, K, 61), _rand(K, N, 62)
+    ref = O.matmul(A.double(), B.double()).float()
+    Ag = (A.t().contiguous().to(cuda).t() if ta else A.to(cuda))
+    Bg = (B.t().contiguous().to(cuda).t() if tb else B.to(cuda))
+    assert ops.gemm_path(Ag, Bg, precision="bf16") == "bf16"
+    out = gemm(Ag, Bg, precision="bf16")
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < TOL_BF16, (O.rel_fro(out, ref), O.rel_max(out, ref))
+    # against the product of the rounded operands the error is only the fp32 accumulation
+    ref16 = O.matmul(A.bfloat16().double(), B.bfloat16().double()).float()
+    assert O.rel_fro(out, ref16) < 1e-5, O.rel_fro(out, ref16)
+
+
+def test_bf16_conversion_rounds_to_nearest_even(cuda):
+    from graphcuda_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(257, 131, generator=g) * torch.logspace(-20, 20, 131)
+    X[0, :4] = torch.tensor([float("inf"), -float("inf"), 0.0, -0.0])
+    X[1, 0] = 1.00390625  # exactly between two bf16 values: ties to even
+    Y = ops.to_bf16(X.to(cuda))
+    assert Y.dtype == torch.bfloat16 and Y.shape == X.shape and Y.stride(0) == 136
+    assert torch.equal(Y.cpu(), X.bfloat16())
+    Yt = ops.to_bf16(X.to(cuda), transpose=True)
+    assert Yt.shape == (131, 257) and torch.equal(Yt.cpu(), X.t().bfloat16())
+
+
+def test_bf16_weight_gradient_and_epilogue(cuda):
+    from graphcuda_b200 import gemm, ops
+    A, G = _rand(100_000, 96, 71), _rand(100_000, 256, 72)  # (A X)^T G: few tiles, K split across CTAs
+    ref = O.matmul(A.t().double(), G.double()).float()
+    out = gemm(A.to(cuda).t(), G.to(cuda), precision="bf16")
+    ops.check_gemm_flag(cuda)
+    assert O.rel_fro(out, ref) < TOL_BF16
+    assert torch.equal(out, gemm(A.to(cuda).t(), G.to(cuda), precision="bf16"))
+    X, W, b = _rand(5000, 128, 73), _rand(128, 256, 74), _rand(1, 256, 75)[0]
+    pre = O.matmul(X.double(), W.double()).float() + b
+    gate = _rand(5000, 256, 76)
+    Y = gemm(X.to(cuda), W.to(cuda), bias=b.to(cuda), relu=True, precision="bf16", gate=gate.to(cuda))
+    assert O.rel_fro(Y, pre * (pre > 0) * (gate > 0)) < 2 * TOL_BF16  # ReLU flips near zero add a little
+
+
+def test_bf16_dense_adjacency_keeps_one_converted_copy(cuda):
+    import graphcuda_b200 as gc
+    from graphcuda_b200 import ops
+    n, F = 3000, 64
+    A = (_rand(n, n, 81) > 0.98).float() * _rand(n, n, 82).abs()
+    A = (A + A.t()).to(cuda)
+    H = _rand(n, F, 83).to(cuda)
+    b = _rand(1, F, 84)[0].to(cuda)
+    dadj = gc.DenseAdjacency(A, symmetric=True)
+    Y = dadj.matmul(H, bias=b, relu=True, precision="bf16")
+    ops.check_gemm_flag(cuda)
+    pre = A.double().cpu() @ H.double().cpu() + b.double().cpu()
+    assert O.rel_fro(Y, pre * (pre > 0)) < 2 * TOL_BF16
+    memo = A._gc_bf16
+    dadj.matmul(H, precision="bf16")
+    assert A._gc_bf16 is memo  # not converted again
+    A[0, 1] += 1.0             # an in-place change invalidates the copy
+    dadj.matmul(H, precision="bf16")
+    assert A._gc_bf16 is not memo

@@ -31,7 +31,7 @@ def _inputs(n, dims):
     return A, X, y
 
 
-def _worker(rank, world, port, n, dims, q, mode):
+def _worker(rank, world, port, n, dims, q, mode, exchange="auto", steps=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -40,21 +40,29 @@ def _worker(rank, world, port, n, dims, q, mode):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         from graphcuda_b200 import CSRAdjacency
-        from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, PartitionedGraph
+        from graphcuda_b200.partition import DistGCN, FeatureShardedGraph, HybridGraph, PartitionedGraph
         A, X, y = _inputs(n, dims)
-        rowptr, col, val = O.coo_to_csr_int32(A)
+        rowptr, col, val = (t.to(dev) for t in O.coo_to_csr_int32(A))
         if mode == "rows":
-            graph = PartitionedGraph(rowptr.to(dev), col.to(dev), val.to(dev), n)
+            graph = PartitionedGraph(rowptr, col, val, n, exchange=exchange)
+        elif mode == "rows-nnz":
+            graph = PartitionedGraph(rowptr, col, val, n, exchange=exchange, balance="nnz")
+        elif mode == "hybrid":
+            graph = HybridGraph(rowptr, col, val, CSRAdjacency(rowptr, col, val, (n, n)), n, exchange=exchange,
+                                wide_from=32)
         else:
-            graph = FeatureShardedGraph(CSRAdjacency(rowptr.to(dev), col.to(dev), val.to(dev), (n, n)), n)
+            graph = FeatureShardedGraph(CSRAdjacency(rowptr, col, val, (n, n)), n, exchange=exchange)
+        assert (graph.symm is not None) == (exchange == "auto")  # peer-memory exchange really in use
         lo, hi = graph.lo, graph.hi
         torch.manual_seed(5)
         model = DistGCN(dims).to(dev)
-        Xl = X[lo:hi].to(dev).requires_grad_()
-        Xg = graph.prepare_constant(Xl.detach())
-        out = model(Xl, graph, X_gathered=Xg)
-        loss = torch.nn.functional.nll_loss(out, y[lo:hi].to(dev), reduction="sum") / n
-        loss.backward()
+        Xg = graph.prepare_constant(X[lo:hi].to(dev))
+        for _ in range(steps):  # repeated steps reuse every exchange buffer: stale or torn contents would show
+            model.zero_grad()
+            Xl = X[lo:hi].to(dev).requires_grad_()
+            out = model(Xl, graph, X_gathered=Xg)
+            loss = torch.nn.functional.nll_loss(out, y[lo:hi].to(dev), reduction="sum") / n
+            loss.backward()
         torch.cuda.synchronize()
         q.put((rank, lo, hi, out.detach().cpu(), Xl.grad.cpu(), [w.grad.cpu() for w in model.weights]))
         dist.barrier()
@@ -63,15 +71,18 @@ def _worker(rank, world, port, n, dims, q, mode):
 
 
 @pytest.mark.parametrize("n,dims", [(5000, [24, 32, 32, 7]), (3001, [40, 16, 5]), (4000, [24, 128, 256, 7])])
-@pytest.mark.parametrize("mode", ["rows", "features"])
-def test_two_gpu_partition_matches_oracle(n, dims, mode):
+@pytest.mark.parametrize("mode,exchange", [("rows", "auto"), ("features", "auto"), ("hybrid", "auto"),
+                                           ("rows-nnz", "auto"), ("rows", "collective"), ("features", "collective")])
+def test_two_gpu_partition_matches_oracle(n, dims, mode, exchange):
+    """exchange "auto": blocks pulled / slabs pushed through peer-mapped symmetric memory; "collective": NCCL's
+    all_gather_into_tensor / all_to_all_single.  Three steps on the same buffers, the last one compared."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode, exchange, 3)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in range(world)]

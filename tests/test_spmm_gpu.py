@@ -238,3 +238,47 @@ def test_gather_sum_probe_is_a_real_sum(cuda, F, deg, in_flight):
                              torch.cuda.current_stream().cuda_stream)
     assert st == 0, L.gc_last_error()
     assert O.rel_fro(Y, ref) < 1e-5
+
+
+@pytest.mark.parametrize("F,n_blocks", [(32, 4), (8, 8), (100, 3), (256, 2), (7, 5)])
+def test_rows_stored_into_per_owner_blocks(cuda, F, n_blocks):
+    """gc_spmm_csr_f32_blocks: row i goes to block i // block_rows, row i % block_rows -- here the blocks are
+    column slices of local matrices (as the owners' buffers are in the multi-GPU scheme), long rows included."""
+    M, K = 1003, 4000
+    A = random_csr(M, K, 7.0, seed=F, long_rows=((5, 3000), (1002, 2500)), empty_rows=(0,))
+    H = torch.randn(K, F, generator=torch.Generator().manual_seed(1))
+    b = torch.randn(F, generator=torch.Generator().manual_seed(2))
+    pre = O.spmm(A, H) + b
+    ref = pre * (pre > 0)
+    adj = to_gpu_csr(A, cuda)
+    B = -(-M // n_blocks)
+    wide = [torch.full((B, F + 12), float("nan"), device=cuda) for _ in range(n_blocks)]
+    blocks = [w[:, 4:4 + F] for w in wide]  # views with a larger row stride and a column offset
+    adj.matmul_into_blocks(H.to(cuda), blocks, B, bias=b.to(cuda), relu=True)
+    out = torch.cat([blk for blk in blocks])[:M]
+    assert O.rel_fro(out, ref) < TOL and O.rel_max(out, ref) < TOL
+    for w in wide:  # nothing outside the slices was touched
+        assert bool(torch.isnan(w[:, :4]).all()) and bool(torch.isnan(w[:, 4 + F:]).all())
+    assert bool(torch.isnan(torch.cat(blocks)[M:]).all())  # rows past M of the last block too
+
+
+@pytest.mark.parametrize("F", [8, 16, 48, 64, 104, 128, 256, 520])
+def test_bf16_gathers_sum_in_fp32(cuda, F):
+    """H held in bf16 (reduced-precision tier, 1e-2): against the float64 product the error is that of rounding
+    H; against the product of the rounded H only the fp32 summation order differs."""
+    from graphcuda_b200 import ops
+    A = random_csr(3000, 5000, 9.0, seed=F, long_rows=((7, 3000), (100, 2049)), empty_rows=(0, 13))
+    H = torch.randn(5000, F, generator=torch.Generator().manual_seed(F + 1))
+    b = torch.randn(F, generator=torch.Generator().manual_seed(3))
+    adj = to_gpu_csr(A, cuda)
+    H16 = ops.to_bf16(H.to(cuda))
+    out = adj.matmul(H16)
+    assert out.dtype == torch.float32
+    assert O.rel_fro(out, O.spmm(A, H)) < 1e-2
+    assert O.rel_fro(out, O.spmm(A.double(), H.bfloat16().double())) < 1e-5
+    pre = O.spmm(A.double(), H.bfloat16().double()) + b.double()
+    out2 = adj.matmul(H16, bias=b.to(cuda), relu=True)
+    assert O.rel_fro(out2, pre * (pre > 0)) < 1e-5
+    assert torch.equal(out, adj.matmul(H16))
+    with pytest.raises(RuntimeError):
+        adj.matmul(H.to(cuda).bfloat16()[:, :F - 1])  # widths must be multiples of 8
