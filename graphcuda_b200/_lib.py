@@ -52,6 +52,13 @@ SIGNATURES = {
                                 _void, _size, _void]),
     "gc_gemm_resolve_precision": (_int, [_int, _int, _i64, _i64, _i64, _i64, _i64, _i64, _int]),
     "gc_gemm_check_flag": (_int, [_void, _void]),
+    "gc_gcn_layer_workspace_bytes": (_size, [_i64, _i64, _i64, _i64, _int, _int]),
+    "gc_gcn_conv_forward_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _i64, _f32p,
+                                           _int, _f32p, _i64, _f32p, _f32p, _i64, _void, _i64, _i64, _i64, _int,
+                                           _void, _size, _void]),
+    "gc_gcn_conv_backward_csr_f32": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _i64, _f32p,
+                                            _i64, _int, _f32p, _i64, _f32p, _i64, _f32p, _i64, _f32p, _i64, _void,
+                                            _i64, _i64, _i64, _int, _void, _size, _void]),
     "gc_relu_backward_f32": (_int, [_f32p, _i64, _f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
     "gc_mask_mul_f32": (_int, [_f32p, _i64, _f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
     "gc_transpose_f32": (_int, [_f32p, _i64, _f32p, _i64, _i64, _i64, _void]),
@@ -79,6 +86,8 @@ SPMM_MAX_BLOCKS = 16
 EPI_RELU = 1
 EPI_ACCUMULATE = 2
 EPI_TRANSPOSED_OUT = 4
+LAYER_RELU = 1
+LAYER_TRANSFORM_FIRST = 2
 PREC_AUTO = -1
 PREC_FP32_SIMT = 0
 PREC_TF32X3 = 1

@@ -31,6 +31,7 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_tcgen05.cu",
     "elementwise.cu",
+    "gcn_layer.cu",
     "graph_build.cu",
     "loss.cu", "optim.cu",
 ]

@@ -10,11 +10,18 @@ namespace {
 int resolve(bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
             int precision) {
   if (precision == GC_PREC_FP32_SIMT) return GC_PREC_FP32_SIMT;
-  if (precision == GC_PREC_BF16) {  // operands are converted into the workspace: no alignment demands on the inputs
-    if (M <= 0 || N <= 0 || K <= 0) return gc::fail(GC_ERR_UNSUPPORTED, "bf16 GEMM needs non-empty sizes");
-    return GC_PREC_BF16;
-  }
   const bool tc_ok = gc::tc_supported(ta, tb, M, N, K, lda, ldb, ldc);
+  if (precision == GC_PREC_BF16) {
+    // The reduced-precision tier picks the faster of its two engines.  bf16 MMAs run at twice the TF32 rate but
+    // both fp32 operands are first converted into the workspace (read 4 + write 2 + read 2 bytes per element where
+    // the TF32 kernel reads 4): that pays only for compute-bound products.  Measured: 4096^3 (683 flop/byte)
+    // 0.196 ms bf16 against 0.236 ms TF32, 2048^3 (341) 0.050 against 0.042, 2^20 x 256 x 256 (64) 0.77 against 0.39.
+    if (M <= 0 || N <= 0 || K <= 0) return gc::fail(GC_ERR_UNSUPPORTED, "bf16 GEMM needs non-empty sizes");
+    const double flops = 2.0 * double(M) * double(N) * double(K);
+    const double bytes = 4.0 * (double(M) * double(K) + double(K) * double(N) + double(M) * double(N));
+    if (tc_ok && flops < 512.0 * bytes) return GC_PREC_TF32;
+    return GC_PREC_BF16;  // operands are converted into the workspace: no alignment demands on the inputs
+  }
   if (precision == GC_PREC_TF32X3 || precision == GC_PREC_TF32) {
     if (!tc_ok)
       return gc::fail(GC_ERR_UNSUPPORTED,
@@ -50,7 +57,7 @@ size_t gc_gemm_workspace_bytes(int transA, int transB, int64_t M, int64_t N, int
     case GC_PREC_FP32_SIMT: return std::max<size_t>(simt, 256);
     case GC_PREC_TF32X3: return tc3;
     case GC_PREC_TF32: return tc1;
-    case GC_PREC_BF16: return gc::bf16_workspace_bytes(M, N, std::max<int64_t>(K, 1));
+    case GC_PREC_BF16: return std::max(tc1, gc::bf16_workspace_bytes(M, N, std::max<int64_t>(K, 1)));
     default: return std::max(std::max(simt, tc3), size_t(256));
   }
 }

@@ -251,7 +251,9 @@ spmm_pieces_kernel(const int32_t* __restrict__ rowptr, const int32_t* __restrict
   Epilogue my_ep = ep;
   if (!direct) my_ep = Epilogue{nullptr, nullptr, nullptr, 0, 0};
 
-  for (int f0 = 0; f0 < F; f0 += PASS) {
+  // Feature columns beyond one pass are walked in turn -- or, when the matrix has too few pieces to fill the
+  // GPU (a Cora-sized graph with a 1433-wide H), spread over gridDim.y so that the passes run side by side.
+  for (int f0 = blockIdx.y * PASS; f0 < F; f0 += gridDim.y * PASS) {
     typename V::T acc[NACC];
     bool live[NACC];
 #pragma unroll
@@ -629,7 +631,11 @@ void launch_pieces(bool planned, const int32_t* rowptr, const int32_t* col, cons
                    float* Y, int64_t ldY, float* scratch, int64_t ldS, int cap, int32_t* ovf, const Epilogue& ep,
                    const RowBlocks& rb, cudaStream_t st) {
   constexpr int PER_CTA = 256 / GROUP;
-  const unsigned grid = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
+  const unsigned gx = unsigned((n_pieces + PER_CTA - 1) / PER_CTA);
+  const int passes = (F + GROUP * NACC * VW - 1) / (GROUP * NACC * VW);
+  // few pieces and several passes: one CTA row per pass (up to about eight CTAs per SM in total)
+  const unsigned gy = unsigned(std::max(1, std::min<int>(passes, int(gc::kNumSMs * 8 / std::max(gx, 1u)))));
+  const dim3 grid(gx, gy);
   constexpr int MINB = pieces_min_ctas(GROUP, NACC, VW);
   if (planned)
     spmm_pieces_kernel<GROUP, NACC, VW, U, true, MINB>

@@ -58,9 +58,8 @@ def _adj_matmul(adj, H, precision, **kw):
     from .adjacency import DenseAdjacency
     if isinstance(adj, DenseAdjacency):
         return adj.matmul(H, precision=precision, **kw)
-    if (precision or ops.get_default_precision()) == "bf16" and H.size(1) % 8 == 0 and H.size(1) >= 8:
-        # reduced-precision tier: the aggregation gathers a bf16 copy of H (half the bytes), sums in fp32
-        return adj.matmul(ops.to_bf16(H), **kw)
+    # (The aggregation accepts a bf16 H -- CSRAdjacency.matmul(ops.to_bf16(H)) -- but converting an fp32 H for one
+    # product costs about what the narrower gathers save, so the layer keeps fp32 gathers in every tier.)
     return adj.matmul(H, **kw)
 
 

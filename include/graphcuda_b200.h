@@ -229,8 +229,11 @@ int gc_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const flo
 #define GC_PREC_FP32_SIMT 0    /* IEEE fp32 FMA on CUDA cores, fixed summation order */
 #define GC_PREC_TF32X3 1       /* tcgen05 kind::tf32, split operands, three MMA passes, fp32 accumulate in TMEM */
 #define GC_PREC_TF32 2         /* tcgen05 kind::tf32, one pass (opt-in, 1e-2 tolerance tier) */
-#define GC_PREC_BF16 3         /* tcgen05 kind::f16 on bf16 copies of both operands made in the workspace, fp32
-                                  accumulate (opt-in, 1e-2 tolerance tier; twice the TF32 tensor rate) */
+#define GC_PREC_BF16 3         /* opt-in, 1e-2 tolerance tier: tcgen05 kind::f16 on bf16 copies of both operands made
+                                  in the workspace, fp32 accumulate (twice the TF32 tensor rate) when the product is
+                                  compute-bound (>= 512 flop per operand byte); memory-bound products run as
+                                  GC_PREC_TF32, which reads the fp32 operands in place
+                                  (gc_gemm_resolve_precision tells which) */
 
 #define GC_EPI_TRANSPOSED_OUT 4 /* store C transposed: C is N x M with leading dimension ldc (mask likewise) */
 
@@ -268,6 +271,44 @@ int gc_gemm_bf16_f32(int64_t M, int64_t N, int64_t K,
  * at the start of the workspace.  Synchronises `stream`, reads it back and
  * returns GC_OK or GC_ERR_DEVICE_FLAG (debug / test use). */
 int gc_gemm_check_flag(const void* workspace, void* stream);
+
+/* ---- the layer as one call (reference gcn.cu:5-52) ------------------------ */
+
+/*
+ * Replaces: gcn_conv_forward (src/graphcuda/cuda/gcn.cu:5-25; signature gcn.cuh:6-10) and gcn_conv_backward
+ * (gcn.cu:27-52; gcn.cuh:12-18), ATen twins src/graphcuda/cpp/gcn.cpp:4-41, for a CSR adjacency.
+ *
+ *   forward   Y[n,out] = relu((A X) W + bias);  mask[n,out] = (pre-activation > 0) as 0/1 floats (may be null)
+ *   backward  G = dY * mask;  dW[in,out] = (A X)^T G;  dX[n,in] = A (G W^T)       (A, not A^T: gcn.cu:49)
+ *
+ * flags: GC_LAYER_RELU = the reference's apply_relu.  GC_LAYER_TRANSFORM_FIRST = compute A (X W) (and
+ * S = A G, dW = X^T S, dX = S W^T backward) so that the aggregation runs on the output width; the caller
+ * asserts that A is symmetric (gc_csr_is_symmetric), for which the two orders agree up to rounding.
+ * AX (n x in, leading dimension ldax): in the aggregate-first order the forward call writes A X there and the
+ * backward call reads it; backward accepts null and then recomputes A X as the reference does (gcn.cu:40).
+ * dX or dW may be null (not computed; the reference always computes both).  bias may be null (the reference has
+ * none).  plan / n_pieces / n_slots / n_cut: as for gc_spmm_csr_f32 (plan may be null).
+ * workspace: gc_gcn_layer_workspace_bytes(n, in, out, n_slots, precision, backward) bytes, 256-byte aligned,
+ * zero-filled once before its first use (the GEMM keeps a sticky error word in it).
+ */
+#define GC_LAYER_RELU 1
+#define GC_LAYER_TRANSFORM_FIRST 2
+size_t gc_gcn_layer_workspace_bytes(int64_t n, int64_t in_dim, int64_t out_dim, int64_t n_slots, int precision,
+                                    int backward);
+int gc_gcn_conv_forward_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
+                                int64_t n, int64_t in_dim, int64_t out_dim,
+                                const float* X, int64_t ldx, const float* W, int64_t ldw, const float* bias,
+                                int flags, float* Y, int64_t ldy, float* mask, float* AX, int64_t ldax,
+                                const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                                int precision, void* workspace, size_t workspace_bytes, void* stream);
+int gc_gcn_conv_backward_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
+                                 int64_t n, int64_t in_dim, int64_t out_dim,
+                                 const float* dY, int64_t lddy, const float* X, int64_t ldx,
+                                 const float* W, int64_t ldw, int flags,
+                                 const float* mask, int64_t ldmask, const float* AX, int64_t ldax,
+                                 float* dX, int64_t lddx, float* dW, int64_t lddw,
+                                 const void* plan, int64_t n_pieces, int64_t n_slots, int64_t n_cut,
+                                 int precision, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- ReLU mask helpers (reference gcn.cu:19-20,36) ----------------------- */
 

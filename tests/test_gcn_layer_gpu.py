@@ -392,3 +392,59 @@ def test_evaluate_matches_the_scripts_test_function(cuda):
     assert [c[1] for c in got] == [140, 500, 1000]
     # no autograd state is kept by the evaluation pass
     assert all(p.grad is None for p in model.parameters())
+
+
+@pytest.mark.parametrize("order", ["aggregate_first", "transform_first"])
+@pytest.mark.parametrize("relu,recompute", [(True, False), (False, False), (True, True)])
+def test_layer_entry_points_of_the_c_abi(cuda, order, relu, recompute):
+    """gc_gcn_conv_forward_csr_f32 / gc_gcn_conv_backward_csr_f32 called with raw pointers, as a C++ binding of the
+    ABI would: the reference's two layer functions (gcn.cu:5-52) against the oracle, in both product orders, with
+    and without ReLU, with A X kept from the forward call or recomputed like the reference does."""
+    from graphcuda_b200 import _lib
+    from tests.helpers import to_gpu_csr, untie
+    L = _lib.lib()
+    n, fin, fout = 3000, 40, 24
+    A = _graph(n, 10, seed=4)
+    g = torch.Generator().manual_seed(8)
+    X = torch.randn(n, fin, generator=g)
+    W = (torch.rand(fin, fout, generator=g) * 2 - 1) * 0.3
+    dY = torch.randn(n, fout, generator=g)
+    Yr, mask_r = O.gcn_conv_forward(X, A, W, relu)
+    if relu:
+        dY = untie(dY, A.mm(X).mm(W))
+    dXr, dWr = O.gcn_conv_backward(dY, X, A, W, relu, mask_r)
+    adj = to_gpu_csr(A, cuda)
+    plan = adj.plan_for(max(fin, fout))
+    flags = (_lib.LAYER_RELU if relu else 0) | (_lib.LAYER_TRANSFORM_FIRST if order == "transform_first" else 0)
+    Xg, Wg, dYg = X.to(cuda), W.to(cuda), dY.to(cuda)
+    Y = torch.empty(n, fout, device=cuda)
+    mask = torch.empty(n, fout, device=cuda)
+    AX = torch.empty(n, fin, device=cuda)
+    s = torch.cuda.current_stream().cuda_stream
+    P = _lib.PREC_FP32_SIMT
+    wsf = torch.zeros(L.gc_gcn_layer_workspace_bytes(n, fin, fout, plan.n_slots, P, 0), dtype=torch.uint8, device=cuda)
+    st = L.gc_gcn_conv_forward_csr_f32(adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), n, fin, fout,
+                                       Xg.data_ptr(), fin, Wg.data_ptr(), fout, None, flags, Y.data_ptr(), fout,
+                                       mask.data_ptr(), AX.data_ptr(), fin, plan.buf.data_ptr(), plan.n_pieces,
+                                       plan.n_slots, plan.n_cut, P, wsf.data_ptr(), wsf.numel(), s)
+    assert st == 0, L.gc_last_error()
+    assert O.rel_fro(Y, Yr) < TOL
+    if order == "aggregate_first":
+        assert O.rel_fro(AX, A.mm(X)) < TOL
+    dX = torch.empty(n, fin, device=cuda)
+    dW = torch.empty(fin, fout, device=cuda)
+    wsb = torch.zeros(L.gc_gcn_layer_workspace_bytes(n, fin, fout, plan.n_slots, P, 1), dtype=torch.uint8, device=cuda)
+    keep_ax = order == "aggregate_first" and not recompute
+    st = L.gc_gcn_conv_backward_csr_f32(adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), n, fin, fout,
+                                        dYg.data_ptr(), fout, Xg.data_ptr(), fin, Wg.data_ptr(), fout, flags,
+                                        mask.data_ptr() if relu else None, fout,
+                                        AX.data_ptr() if keep_ax else None, fin, dX.data_ptr(), fin, dW.data_ptr(),
+                                        fout, plan.buf.data_ptr(), plan.n_pieces, plan.n_slots, plan.n_cut, P,
+                                        wsb.data_ptr(), wsb.numel(), s)
+    assert st == 0, L.gc_last_error()
+    assert O.rel_fro(dX, dXr) < TOL and O.rel_fro(dW, dWr) < TOL
+    # a workspace that is too small is refused before anything is launched
+    assert L.gc_gcn_conv_forward_csr_f32(adj.rowptr.data_ptr(), adj.col.data_ptr(), adj.val.data_ptr(), n, fin, fout,
+                                         Xg.data_ptr(), fin, Wg.data_ptr(), fout, None, flags, Y.data_ptr(), fout,
+                                         None, AX.data_ptr(), fin, plan.buf.data_ptr(), plan.n_pieces, plan.n_slots,
+                                         plan.n_cut, P, wsf.data_ptr(), 1024, s) == -4

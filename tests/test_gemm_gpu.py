@@ -212,8 +212,9 @@ def test_bf16_tier_all_layouts(cuda, shape, ta, tb):
     ref = O.matmul(A.double(), B.double()).float()
     Ag = (A.t().contiguous().to(cuda).t() if ta else A.to(cuda))
     Bg = (B.t().contiguous().to(cuda).t() if tb else B.to(cuda))
-    assert ops.gemm_path(Ag, Bg, precision="bf16") == "bf16"
-    out = gemm(Ag, Bg, precision="bf16")
+    # gemm(precision="bf16") takes the bf16 engine for compute-bound products only; here the engine itself is
+    # exercised on every shape: operands converted (and re-laid K-major) exactly as gc_gemm_f32 does, then multiplied
+    out = ops.gemm_bf16_operands(ops.to_bf16(Ag), ops.to_bf16(Bg, transpose=True))
     ops.check_gemm_flag(cuda)
     assert O.rel_fro(out, ref) < TOL_BF16, (O.rel_fro(out, ref), O.rel_max(out, ref))
     # against the product of the rounded operands the error is only the fp32 accumulation
@@ -235,18 +236,38 @@ def test_bf16_conversion_rounds_to_nearest_even(cuda):
 
 
 def test_bf16_weight_gradient_and_epilogue(cuda):
-    from graphcuda_b200 import gemm, ops
+    from graphcuda_b200 import ops
     A, G = _rand(100_000, 96, 71), _rand(100_000, 256, 72)  # (A X)^T G: few tiles, K split across CTAs
     ref = O.matmul(A.t().double(), G.double()).float()
-    out = gemm(A.to(cuda).t(), G.to(cuda), precision="bf16")
+    A16, G16 = ops.to_bf16(A.to(cuda), transpose=True), ops.to_bf16(G.to(cuda), transpose=True)
+    out = ops.gemm_bf16_operands(A16, G16)
     ops.check_gemm_flag(cuda)
     assert O.rel_fro(out, ref) < TOL_BF16
-    assert torch.equal(out, gemm(A.to(cuda).t(), G.to(cuda), precision="bf16"))
+    assert torch.equal(out, ops.gemm_bf16_operands(A16, G16))
     X, W, b = _rand(5000, 128, 73), _rand(128, 256, 74), _rand(1, 256, 75)[0]
     pre = O.matmul(X.double(), W.double()).float() + b
     gate = _rand(5000, 256, 76)
-    Y = gemm(X.to(cuda), W.to(cuda), bias=b.to(cuda), relu=True, precision="bf16", gate=gate.to(cuda))
+    Y = ops.gemm_bf16_operands(ops.to_bf16(X.to(cuda)), ops.to_bf16(W.to(cuda), transpose=True), bias=b.to(cuda),
+                               relu=True, gate=gate.to(cuda))
     assert O.rel_fro(Y, pre * (pre > 0) * (gate > 0)) < 2 * TOL_BF16  # ReLU flips near zero add a little
+
+
+def test_bf16_tier_picks_its_engine_by_arithmetic_intensity(cuda):
+    """precision="bf16" is the reduced-precision tier: bf16 MMAs where the product is compute-bound, single-pass
+    TF32 (fp32 operands read in place) where converting the operands would cost more than the faster MMAs save."""
+    from graphcuda_b200 import gemm, ops
+    sq = torch.empty(4096, 4096, device=cuda)
+    assert ops.gemm_path(sq, sq, precision="bf16") == "bf16"
+    tall = torch.empty(1 << 18, 256, device=cuda), torch.empty(256, 256, device=cuda)
+    assert ops.gemm_path(*tall, precision="bf16") == "tf32"
+    odd = torch.empty(3000, 4099, device=cuda), torch.empty(4099, 3000, device=cuda)  # pitches TF32 cannot read in place
+    assert ops.gemm_path(*odd, precision="bf16") == "bf16"
+    A, B = _rand(4096, 4096, 91).to(cuda), _rand(4096, 4096, 92).to(cuda)
+    out = gemm(A, B, precision="bf16")
+    ops.check_gemm_flag(cuda)
+    rows = torch.arange(0, 4096, 64, device=cuda)
+    ref = A[rows].double() @ B.double()
+    assert O.rel_fro(out[rows], ref) < TOL_BF16
 
 
 def test_bf16_dense_adjacency_keeps_one_converted_copy(cuda):

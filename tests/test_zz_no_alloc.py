@@ -13,6 +13,7 @@ Collected last on purpose: a failure here does not hide any other test.
 import pytest
 import torch
 
+from oracle import gcn_oracle as O
 from tests.helpers import random_csr, to_gpu_csr
 
 pytestmark = pytest.mark.gpu
@@ -51,6 +52,9 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(cuda):
             torch.cuda.synchronize()
             assert torch.equal(Y, expect)  # same kernels, same order of additions: bit-identical
             assert torch.allclose(Y, expect, rtol=1e-4, atol=1e-6)
+            # and against the CPU oracle directly, not only through the ordinary entry point
+            pre = O.spmm(A, H.cpu()) + b.cpu()
+            assert O.rel_fro(Y, pre * (pre > 0) if relu else pre) < 1e-4
 
 
 def test_noalloc_refuses_what_does_not_fit(cuda):
