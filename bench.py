@@ -634,8 +634,10 @@ def run_ours(args):
     e1 = torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    t_host = time.perf_counter()
     for _ in range(args.steps):
         loss = step(X, y, X_gathered)
+    enqueue_ms = (time.perf_counter() - t_host) * 1e3 / max(args.steps, 1)  # host time to issue a step (no sync)
     e1.record()
     barrier()
     timer.active = False
@@ -741,7 +743,7 @@ def run_ours(args):
         "traffic_note": "bytes per F=256 launch at full size on 1 GPU; compulsory 6.04e9",
     }
 
-    if world == 1 and args.shrink == 1 and per_f.get(256):
+    if world == 1 and per_f.get(256):
         # what the memory system can deliver for this access pattern, beside what the aggregation gets
         try:
             gc_ = gather_ceiling(dev, n, 256)
@@ -766,6 +768,7 @@ def run_ours(args):
                        "in flight while step i computes, the first copy of the timed region is exposed",
                 "value_without_prefetch": e2e_times[False]},
         "gpu_launches": int(launches), "clocks": clocks, "final_loss": final_loss, "setup_s": setup_s,
+        "host_enqueue_ms_per_step": enqueue_ms,
         "partition": (args.partition if world > 1 else "none"),
         "exchange": (("peer copies through symmetric memory" if part.symm is not None else "NCCL collectives")
                      if world > 1 else "none"),

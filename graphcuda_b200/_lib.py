@@ -40,6 +40,7 @@ SIGNATURES = {
                                      _f32p, _f32p, _void, _i64, _i64, _i64, _void, _size, _void]),
     "gc_spmm_csr_f32_blocks": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _void, _int,
                                       _i64, _i64, _void, _i64, _i64, _i64, _void, _size, _void]),
+    "gc_scatter_column_slabs_f32": (_int, [_f32p, _i64, _i64, _i64, _i64, _void, _int, _i64, _void]),
     "gc_gather_sum_f32": (_int, [_f32p, _i64, _i64, _i64, _i32p, _i64, _i64, _f32p, _i64, _int, _void]),
     "gc_spmm_csr_f32_noalloc": (_int, [_i32p, _i32p, _f32p, _i64, _i64, _i64, _f32p, _i64, _f32p, _int, _f32p,
                                        _i64, _f32p, _f32p, _void, _i64, _i64, _i64, _void]),

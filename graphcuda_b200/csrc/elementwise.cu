@@ -80,9 +80,56 @@ int mask_mul(const float* dY, int64_t lddy, const float* S, int64_t lds, float* 
   return gc::check_launch(who);
 }
 
+// Column slabs of a row-major matrix, each to its own destination matrix: dst[q][r, c] = src[r, q * w + c].
+// The destinations may be other GPUs' buffers (peer-mapped memory): the rows -> columns transpose of the
+// feature-sharded multi-GPU scheme as ONE kernel of ordinary loads and stores, every element read once.
+struct SlabDests {
+  float* base[GC_SPMM_MAX_BLOCKS];
+};
+
+template <int VW>
+__global__ void __launch_bounds__(256)
+scatter_slabs_kernel(const float* __restrict__ src, int64_t ld, int64_t rows, int F, int w, int64_t dst_ld,
+                     const __grid_constant__ SlabDests d) {
+  const int per_row = (F + VW - 1) / VW;
+  const int64_t total = rows * per_row;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+    const int64_t r = i / per_row;
+    const int c = int(i % per_row) * VW;
+    const int q = c / w;
+    float* out = d.base[q] + r * dst_ld + (c - q * w);
+    if (VW == 4) {
+      *reinterpret_cast<float4*>(out) = __ldcs(reinterpret_cast<const float4*>(src + r * ld + c));
+    } else {
+      *out = __ldcs(src + r * ld + c);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+int gc_scatter_column_slabs_f32(const float* src, int64_t ld, int64_t rows, int64_t F, int64_t w, float* const* dst,
+                                int n_dst, int64_t dst_ld, void* stream) {
+  GC_REQUIRE(rows >= 0 && F >= 0 && F < INT32_MAX && w >= 1 && w < INT32_MAX, "gc_scatter_column_slabs_f32: bad size");
+  GC_REQUIRE(n_dst >= 1 && n_dst <= GC_SPMM_MAX_BLOCKS && int64_t(n_dst) * w >= F,
+             "gc_scatter_column_slabs_f32: n_dst slabs of w columns must cover F (at most %d slabs)", GC_SPMM_MAX_BLOCKS);
+  if (rows == 0 || F == 0) return GC_OK;
+  GC_REQUIRE(src && dst && ld >= F && dst_ld >= w, "gc_scatter_column_slabs_f32: null pointer or leading dimension");
+  SlabDests d{};
+  bool vec = (w % 4 == 0) && (F % 4 == 0) && (ld % 4 == 0) && (dst_ld % 4 == 0) && gc::aligned16(src);
+  for (int q = 0; q < n_dst; ++q) {
+    GC_REQUIRE(dst[q] || int64_t(q) * w >= F, "gc_scatter_column_slabs_f32: null destination");
+    d.base[q] = dst[q];
+    vec = vec && gc::aligned16(dst[q]);
+  }
+  const int64_t items = rows * (vec ? (F + 3) / 4 : F);
+  const unsigned grid = unsigned(std::min<int64_t>(gc::ceil_div(items, 256), gc::kNumSMs * 16));
+  if (vec) scatter_slabs_kernel<4><<<grid, 256, 0, gc::as_stream(stream)>>>(src, ld, rows, int(F), int(w), dst_ld, d);
+  else scatter_slabs_kernel<1><<<grid, 256, 0, gc::as_stream(stream)>>>(src, ld, rows, int(F), int(w), dst_ld, d);
+  return gc::check_launch("gc_scatter_column_slabs_f32");
+}
 
 int gc_relu_backward_f32(const float* dY, int64_t lddy, const float* Y, int64_t ldy, float* G, int64_t ldg,
                          int64_t M, int64_t N, void* stream) {

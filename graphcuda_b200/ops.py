@@ -266,6 +266,29 @@ def mask_mul(dY: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
     return G
 
 
+def scatter_column_slabs(src: torch.Tensor, dsts, w: int) -> None:
+    """dsts[q][r, c] = src[r, q * w + c]: the column slabs of a row-major float32 matrix, each written to its own
+    destination (float32 views of at least src.size(0) rows with one common row stride; other GPUs' peer-mapped
+    buffers are fine).  One kernel; every element of src is read once."""
+    import ctypes
+    _require(src.dim() == 2 and src.is_cuda and src.dtype == torch.float32, "float32 CUDA matrix expected")
+    src = _row_major(src)
+    rows, F = src.shape
+    _require(1 <= len(dsts) <= _lib.SPMM_MAX_BLOCKS and len(dsts) * w >= F, "slabs must cover the columns")
+    ld = dsts[0].stride(0)
+    for q, d in enumerate(dsts):
+        need = min(w, F - q * w)
+        _require(d.dtype == torch.float32 and d.dim() == 2 and d.stride(1) == 1 and d.stride(0) == ld
+                 and d.size(0) >= rows and (need <= 0 or d.size(1) >= need), "bad slab destination")
+    if rows == 0 or F == 0:
+        return
+    ptrs = (ctypes.c_void_p * len(dsts))(*[d.data_ptr() for d in dsts])
+    with torch.cuda.device(src.device):
+        st = _lib.lib().gc_scatter_column_slabs_f32(src.data_ptr(), _ld(src), rows, F, w, ptrs, len(dsts), ld,
+                                                    _stream(src.device))
+    _lib.check(st, "gc_scatter_column_slabs_f32")
+
+
 def transpose(X: torch.Tensor) -> torch.Tensor:
     _require(X.dim() == 2 and X.is_cuda and X.dtype == torch.float32, "transpose: float32 CUDA matrix expected")
     X = _row_major(X)

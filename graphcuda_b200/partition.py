@@ -131,6 +131,11 @@ class CudaBackend:
     def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
         return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into, out=out)
 
+    def scatter_slabs(self, src, dsts, w):
+        """Column slab q of src into dsts[q] (other GPUs' buffers), one kernel."""
+        from . import ops
+        ops.scatter_column_slabs(src, dsts, w)
+
     def spmm_into_blocks(self, adj, H, blocks, block_rows, *, bias=None, relu=False):
         """The aggregation with its rows stored into per-owner blocks (other GPUs' buffers)."""
         adj.matmul_into_blocks(H, blocks, block_rows, bias=bias, relu=relu)
@@ -495,6 +500,12 @@ class FeatureShardedGraph:
         key = ("r2c", w, tag)
         recv, hdl, peers = self.symm.buffer(key, (P, B, w))
         self.symm.begin(key, hdl)
+        if hasattr(self.backend, "scatter_slabs"):
+            # one kernel reads this rank's rows once and stores slab q into slot `rank` of rank q's buffer
+            if self.rows > 0:
+                self.backend.scatter_slabs(Y_rows, [peers[q][self.rank, :self.rows] for q in range(P)], w)
+            hdl.barrier(channel=0)
+            return recv.view(P * B, w)
         pieces = []
         for k in range(P):
             q = (self.rank + k) % P

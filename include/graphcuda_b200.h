@@ -162,6 +162,16 @@ int gc_spmm_csr_f32_blocks(const int32_t* rowptr, const int32_t* col, const floa
                            void* stream);
 
 /*
+ * dst[q][r, c] = src[r, q * w + c] for the n_dst column slabs of width w of a rows x F matrix (the last slab may be
+ * narrower).  dst is a HOST array of device pointers, each a matrix of leading dimension dst_ld; they may be other
+ * GPUs' peer-mapped buffers.  No counterpart in the reference: it is the rows -> columns transpose that precedes
+ * gc_spmm_csr_f32_blocks in the feature-sharded multi-GPU scheme, as one kernel that reads every element once and
+ * stores it where the rank that aggregates its slab will gather from.
+ */
+int gc_scatter_column_slabs_f32(const float* src, int64_t ld, int64_t rows, int64_t F, int64_t w,
+                                float* const* dst, int n_dst, int64_t dst_ld, void* stream);
+
+/*
  * Measurement aid, no counterpart in the reference: the access pattern of the
  * aggregation above with everything else removed.
  *   Y[i, :] = sum over k < deg of H[idx[i * deg + k], :]      (i < n_rows)

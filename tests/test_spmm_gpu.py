@@ -282,3 +282,18 @@ def test_bf16_gathers_sum_in_fp32(cuda, F):
     assert torch.equal(out, adj.matmul(H16))
     with pytest.raises(RuntimeError):
         adj.matmul(H.to(cuda).bfloat16()[:, :F - 1])  # widths must be multiples of 8
+
+
+@pytest.mark.parametrize("rows,F,w", [(1000, 256, 32), (777, 100, 16), (50, 47, 12), (3, 8, 8), (1200, 96, 96)])
+def test_column_slabs_scattered_to_their_destinations(cuda, rows, F, w):
+    """gc_scatter_column_slabs_f32: the rows -> columns transpose of the feature-sharded scheme in one kernel."""
+    from graphcuda_b200 import ops
+    P = -(-F // w)
+    src = torch.randn(rows, F, generator=torch.Generator().manual_seed(F)).to(cuda)
+    bufs = [torch.full((rows + 5, w + 4), float("nan"), device=cuda) for _ in range(P)]
+    ops.scatter_column_slabs(src, [b[:rows, :w] for b in bufs], w)
+    for q, b in enumerate(bufs):
+        c0, c1 = q * w, min((q + 1) * w, F)
+        assert torch.equal(b[:rows, :c1 - c0], src[:, c0:c1])
+        assert bool(torch.isnan(b[rows:]).all()) and bool(torch.isnan(b[:, w:]).all())
+        assert bool(torch.isnan(b[:rows, c1 - c0:w]).all())  # a short last slab leaves its pad alone
