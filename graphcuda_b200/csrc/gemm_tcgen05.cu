@@ -563,15 +563,39 @@ transpose_kernel(const float* __restrict__ in, int64_t ldin, float* __restrict__
   }
 }
 
-// C = sum over splits of partial[split] (in split order), then the epilogue.
+// C = sum over splits of partial[split], then the epilogue.  The order of the additions is fixed (eight
+// contiguous groups of splits summed in split order by eight warps, the eight group sums added in group order), so
+// the result is the same run to run; the groups run side by side because a capped-chain product has a thousand
+// partial tiles and one thread per element walking them all was latency-bound (0.22 ms for a 100 x 256 result).
 __global__ void __launch_bounds__(256)
 tc_splitk_reduce_kernel(int M, int N, int splits, const float* __restrict__ partial, float* __restrict__ C,
                         int64_t ldc, gc::GemmEpilogue ep) {
+  __shared__ float sm[8][32];
+  const int e = threadIdx.x % 32, g = threadIdx.x / 32;
   const int64_t total = int64_t(M) * N;
-  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
-    float s = partial[i];
-    for (int z = 1; z < splits; ++z) s += partial[int64_t(z) * total + i];
-    gc::epilogue_store(s, int(i / N), int(i % N), C, ldc, ep);
+  const int per = (splits + 7) / 8;
+  const int z0 = g * per, z1 = min(splits, z0 + per);
+  for (int64_t base = int64_t(blockIdx.x) * 32; base < total; base += int64_t(gridDim.x) * 32) {
+    const int64_t i = base + e;
+    float s = 0.f;
+    if (i < total) {
+      int z = z0;
+      for (; z + 4 <= z1; z += 4) {
+        const float a = partial[int64_t(z) * total + i], b = partial[int64_t(z + 1) * total + i],
+                    c = partial[int64_t(z + 2) * total + i], d = partial[int64_t(z + 3) * total + i];
+        s = (((s + a) + b) + c) + d;
+      }
+      for (; z < z1; ++z) s += partial[int64_t(z) * total + i];
+    }
+    sm[g][e] = s;
+    __syncthreads();
+    if (g == 0 && i < total) {
+      float t = sm[0][e];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) t += sm[k][e];
+      gc::epilogue_store(t, int(i / N), int(i % N), C, ldc, ep);
+    }
+    __syncthreads();
   }
 }
 
@@ -592,6 +616,30 @@ cvt_bf16_kernel(const float* __restrict__ src, int64_t lds, uint16_t* __restrict
     const float a = c < Cc ? __ldg(src + int64_t(r) * lds + c) : 0.f;
     const float b = c + 1 < Cc ? __ldg(src + int64_t(r) * lds + c + 1) : 0.f;
     reinterpret_cast<uint32_t*>(dst + int64_t(r) * ldd)[c / 2] = uint32_t(to_bf16(a)) | (uint32_t(to_bf16(b)) << 16);
+  }
+}
+// The same for 16-byte aligned rows: eight elements per thread (two 128-bit loads, one 128-bit store).
+__global__ void __launch_bounds__(256)
+cvt_bf16_vec8_kernel(const float* __restrict__ src, int64_t lds, uint16_t* __restrict__ dst, int64_t ldd, int R, int Cc) {
+  const int64_t oct_per_row = ldd / 8;
+  const int64_t total = int64_t(R) * oct_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+    const int r = int(i / oct_per_row), c = int(i % oct_per_row) * 8;
+    const float* p = src + int64_t(r) * lds + c;
+    float v[8];
+    if (c + 8 <= Cc) {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p + 4));
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = c + k < Cc ? __ldg(p + k) : 0.f;
+    }
+    uint4 o;
+    o.x = uint32_t(to_bf16(v[0])) | (uint32_t(to_bf16(v[1])) << 16);
+    o.y = uint32_t(to_bf16(v[2])) | (uint32_t(to_bf16(v[3])) << 16);
+    o.z = uint32_t(to_bf16(v[4])) | (uint32_t(to_bf16(v[5])) << 16);
+    o.w = uint32_t(to_bf16(v[6])) | (uint32_t(to_bf16(v[7])) << 16);
+    *reinterpret_cast<uint4*>(dst + int64_t(r) * ldd + c) = o;
   }
 }
 __global__ void __launch_bounds__(256)
@@ -876,7 +924,7 @@ int gemm_tc(bool ta, bool tb, int64_t M, int64_t N, int64_t K, const float* A, i
   if (rc != GC_OK) return rc;
   if (pl.splits > 1) {
     const int64_t total = M * N;
-    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 256), kNumSMs * 8));
+    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 32), kNumSMs * 8));
     tc_splitk_reduce_kernel<<<g, 256, 0, st>>>(int(M), int(N), pl.splits, partial, C, ldc, ep);
     rc = check_launch("gemm_tc split-K reduce");
   }
@@ -912,6 +960,8 @@ int convert_bf16(const float* src, int64_t lds, int64_t rows, int64_t cols, uint
   // dst is rows x cols (pitch ldd, even); src is rows x cols, or cols x rows when transpose
   const unsigned grid = kNumSMs * 8;
   if (transpose) cvt_transpose_bf16_kernel<<<grid, 256, 0, st>>>(src, lds, dst, ldd, int(cols), int(rows));
+  else if (lds % 4 == 0 && ldd % 8 == 0 && aligned16(src) && aligned16(dst))
+    cvt_bf16_vec8_kernel<<<grid, 256, 0, st>>>(src, lds, dst, ldd, int(rows), int(cols));
   else cvt_bf16_kernel<<<grid, 256, 0, st>>>(src, lds, dst, ldd, int(rows), int(cols));
   return check_launch("convert to bf16");
 }
@@ -952,7 +1002,7 @@ int gemm_bf16_core(int64_t M, int64_t N, int64_t K, const uint16_t* A, int64_t l
   if (rc != GC_OK) return rc;
   if (p.splits > 1) {
     const int64_t total = M * N;
-    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 256), kNumSMs * 8));
+    const unsigned g = unsigned(std::min<int64_t>(ceil_div(total, 32), kNumSMs * 8));
     tc_splitk_reduce_kernel<<<g, 256, 0, st>>>(int(M), int(N), p.splits, p.partial, C, ldc, ep);
     rc = check_launch("bf16 GEMM split-K reduce");
   }
