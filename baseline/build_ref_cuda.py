@@ -25,7 +25,10 @@ NAME = "graphcuda_ref_cuda"
 
 
 def reference_root() -> str:
-    return os.environ.get("GRAPHCUDA_REFERENCE", "/root/reference")
+    """The mounted reference tree: $GRAPHCUDA_REFERENCE_ROOT, else the directory ``reference`` beside this
+    repository."""
+    default = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return os.environ.get("GRAPHCUDA_REFERENCE_ROOT", default)
 
 
 def built_path():
