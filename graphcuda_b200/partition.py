@@ -280,6 +280,10 @@ class PartitionedGraph:
         if not rows_are_local:
             rowptr, col, val = slice_csr_rows(rowptr, col, val, self.lo, self.hi)
         self.nnz_local_rows = int(col.numel())
+        # this rank's rows over ALL columns (padded space), as one matrix: used when the gathered operand is already
+        # resident (constant inputs), where splitting off the diagonal block buys no overlap; built on first use
+        self._whole_parts = (rowptr, col, val)
+        self._whole = None
         (rp_d, c_d, v_d), (rp_o, c_o, v_o) = split_csr_columns(rowptr, col, val, self.lo, self.hi)
         c_o = self.part.to_padded(c_o)  # the remainder gathers from the all-gathered matrix (padded space)
         self.diag = self.backend.make_adj(rp_d, c_d, v_d, (self.rows, max(self.rows, 0)))
@@ -374,8 +378,13 @@ class PartitionedGraph:
         the fused bias/ReLU.  `gathered` short-circuits the exchange when the
         full matrix is already resident (constant input features)."""
         work = None
-        if gathered is None:
-            gathered, work = self.all_gather_rows_async(H_local, tag)
+        if gathered is not None:
+            if self._whole is None:
+                rp, c, v = self._whole_parts
+                self._whole = self.backend.make_adj(rp, self.part.to_padded(c), v, (self.rows, self.part.padded))
+                self._whole_parts = None
+            return self.backend.spmm(self._whole, gathered, bias=bias, relu=relu)
+        gathered, work = self.all_gather_rows_async(H_local, tag)
         Y = self.backend.spmm(self.diag, H_local)
         if work is not None:
             work.wait()
