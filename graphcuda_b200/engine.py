@@ -13,6 +13,7 @@ the reference's (including its use of A rather than A^T for dX, gcn.cu:49).
 """
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -46,9 +47,23 @@ def _padded_width(n_rows: int, in_dim: int, out_dim: int) -> int:
     return (out_dim + 3) // 4 * 4
 
 
+# Buffers this library produced with zero-filled pad columns, by the address of their first element: the loss
+# backward writes the gradient of a padded logits matrix straight into such a buffer and hands out the unpadded
+# view; the layer below recognises the view here and uses the buffer instead of zero-filling and copying a new one.
+_zero_padded = weakref.WeakValueDictionary()
+
+
+def register_zero_padded(buf: torch.Tensor) -> None:
+    _zero_padded[buf.data_ptr()] = buf
+
+
 def _pad_cols(t: torch.Tensor, width: int) -> torch.Tensor:
     if t.size(-1) == width:
         return t
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) == width:
+        base = _zero_padded.get(t.data_ptr())
+        if base is not None and tuple(base.shape) == (t.size(0), width) and base.is_contiguous():
+            return base
     out = t.new_zeros(t.shape[:-1] + (width,))
     out[..., :t.size(-1)] = t
     return out

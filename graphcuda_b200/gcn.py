@@ -55,7 +55,9 @@ class GCNConvFunction(torch.autograd.Function):
         inter = saved[3] if ctx.has_inter else None
         need_dX, _, need_dW = ctx.needs_input_grad[:3]
         need_db = ctx.has_bias and ctx.needs_input_grad[4]
-        dX, dW, db = layer_backward(grad_Y.contiguous(), X, ctx.adj, weights, ctx.apply_relu, Y,
+        if grad_Y.stride(-1) != 1:  # rows may keep a larger pitch (a padded gradient from the fused loss)
+            grad_Y = grad_Y.contiguous()
+        dX, dW, db = layer_backward(grad_Y, X, ctx.adj, weights, ctx.apply_relu, Y,
                                     (ctx.order, inter), need_dX=need_dX, need_dW=need_dW, need_db=need_db,
                                     precision=ctx.precision, grad_is_gated=bool(ctx.fuse & 1),
                                     gate_dx_by_input=bool(ctx.fuse & 2))

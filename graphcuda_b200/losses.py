@@ -46,13 +46,24 @@ class _LogSoftmaxNLL(torch.autograd.Function):
         Z, labels, ws = ctx.saved_tensors
         M, C = Z.shape
         dev = Z.device
-        dZ = torch.empty((M, C), dtype=torch.float32, device=dev)
-        g = grad_loss.to(torch.float32).contiguous()
         ldz = Z.stride(0) if M > 1 else max(C, 1)
+        lddz = max(C, 1)
+        if M > 1 and C < ldz <= C + 3 and ldz % 4 == 0:
+            # The logits are a view of a matrix padded to 16-byte rows (an odd class count): give the gradient the
+            # same pitch with zero pad columns, so the layer below can aggregate it without re-padding a copy.
+            from .engine import register_zero_padded
+            buf = torch.empty((M, ldz), dtype=torch.float32, device=dev)
+            buf[:, C:].zero_()
+            register_zero_padded(buf)
+            dZ = buf[:, :C]
+            lddz = ldz
+        else:
+            dZ = torch.empty((M, C), dtype=torch.float32, device=dev)
+        g = grad_loss.to(torch.float32).contiguous()
         with torch.cuda.device(dev):
             st = _lib.lib().gc_logsoftmax_nll_backward_f32(
                 Z.data_ptr(), ldz, labels.data_ptr(), ctx.mask8.data_ptr() if ctx.mask8 is not None else None, M, C,
-                ctx.scale, g.data_ptr(), dZ.data_ptr(), max(C, 1), ws.data_ptr(), _stream(dev))
+                ctx.scale, g.data_ptr(), dZ.data_ptr(), lddz, ws.data_ptr(), _stream(dev))
         _lib.check(st, "gc_logsoftmax_nll_backward_f32")
         return dZ, None, None, None
 

@@ -128,8 +128,8 @@ class CudaBackend:
         from .adjacency import CSRAdjacency
         return CSRAdjacency(rowptr.contiguous(), col.contiguous(), val.contiguous(), shape, symmetric=False)
 
-    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
-        return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into, out=out)
+    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None, gate=None):
+        return adj.matmul(H, bias=bias, relu=relu, accumulate_into=accumulate_into, out=out, gate=gate)
 
     def scatter_slabs(self, src, dsts, w):
         """Column slab q of src into dsts[q] (other GPUs' buffers), one kernel."""
@@ -242,7 +242,19 @@ def _resolve_exchange(exchange, group, device, world, rank):
         return None
     if exchange != "auto":
         raise ValueError("exchange must be 'auto', 'collective', None or a SymmExchange")
-    return SymmExchange(group, device, world, rank) if SymmExchange.available(device) else None
+    if not SymmExchange.available(device):
+        return None
+    # Symmetric memory needs peer access between all the GPUs of the group; where it cannot be set up (one rank
+    # failing is enough) every rank falls back to the process group's collectives together.
+    ex, ok = None, 1
+    try:
+        ex = SymmExchange(group, device, world, rank)
+        ex.buffer(("probe",), (256,))
+    except Exception:
+        ok = 0
+    flag = torch.tensor([ok], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return ex if int(flag.item()) == 1 else None
 
 
 # ---------------------------------------------------------------- partitioned graph
@@ -372,23 +384,30 @@ class PartitionedGraph:
         return buf.clone()
 
     # -- aggregation ----------------------------------------------------------
-    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a"):
+    def fuses_gate(self, F: int) -> bool:
+        """Whether aggregate(..., gate=) applies the gate in the aggregation's own store (else the caller does)."""
+        return True
+
+    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a", gate=None):
         """rows_r of A @ H for H given by its local row block: diagonal block
         first (overlapping the all-gather), then the off-diagonal remainder with
         the fused bias/ReLU.  `gathered` short-circuits the exchange when the
-        full matrix is already resident (constant input features)."""
+        full matrix is already resident (constant input features).  gate (this
+        rank's rows, contiguous, shape of the result): the result is multiplied
+        by (gate > 0) in the store of the last launch."""
+        kw = {} if gate is None else {"gate": gate}
         work = None
         if gathered is not None:
             if self._whole is None:
                 rp, c, v = self._whole_parts
                 self._whole = self.backend.make_adj(rp, self.part.to_padded(c), v, (self.rows, self.part.padded))
                 self._whole_parts = None
-            return self.backend.spmm(self._whole, gathered, bias=bias, relu=relu)
+            return self.backend.spmm(self._whole, gathered, bias=bias, relu=relu, **kw)
         gathered, work = self.all_gather_rows_async(H_local, tag)
         Y = self.backend.spmm(self.diag, H_local)
         if work is not None:
             work.wait()
-        return self.backend.spmm(self.offd, gathered, bias=bias, relu=relu, accumulate_into=Y)
+        return self.backend.spmm(self.offd, gathered, bias=bias, relu=relu, accumulate_into=Y, **kw)
 
 
 class FeatureShardedGraph:
@@ -548,6 +567,9 @@ class FeatureShardedGraph:
         return self.rows_to_columns(X_local, tag="x").clone()
 
     # -- aggregation --------------------------------------------------------------
+    def fuses_gate(self, F: int) -> bool:
+        return False  # the rows of the result belong to other ranks: their gate is not here
+
     def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a"):
         """rows_r of A @ H (+bias)(ReLU) for H given by its local row block.
         `gathered` is a column slab from prepare_constant()."""
@@ -626,9 +648,13 @@ class HybridGraph:
     def scheme_for(self, F: int, pre_gathered: bool) -> str:
         return "rows" if (pre_gathered or F < self.wide_from or self.world == 1) else "features"
 
-    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a"):
+    def fuses_gate(self, F: int) -> bool:
+        return self.scheme_for(F, False) == "rows"
+
+    def aggregate(self, H_local: torch.Tensor, *, gathered=None, bias=None, relu=False, tag="a", gate=None):
         if self.scheme_for(H_local.size(1), gathered is not None) == "rows":
-            return self.rows_graph.aggregate(H_local, gathered=gathered, bias=bias, relu=relu, tag=tag)
+            return self.rows_graph.aggregate(H_local, gathered=gathered, bias=bias, relu=relu, tag=tag, gate=gate)
+        assert gate is None
         return self.cols_graph.aggregate(H_local, bias=bias, relu=relu, tag=tag)
 
 
@@ -689,7 +715,8 @@ class DistGCNConvFunction(torch.autograd.Function):
         X, W, Y = saved[:3]
         need_dX = ctx.needs_input_grad[0]
         need_dW = ctx.needs_input_grad[2]
-        dY = dY.contiguous()
+        if dY.stride(-1) != 1:  # rows may keep a larger pitch (a padded gradient from the fused loss)
+            dY = dY.contiguous()
         G = be.relu_backward(dY, Y) if (ctx.apply_relu and not ctx.fuse & 1) else dY
         gate_dx = bool(ctx.fuse & 2)
         dX = dW = db = None
@@ -712,8 +739,12 @@ class DistGCNConvFunction(torch.autograd.Function):
                 dW = graph.all_reduce_sum(be.gemm(AX.t(), G, precision=ctx.precision))
             if need_dX:
                 T = _gemm_into_slot(be, graph, G, W.t(), ctx.precision, W.size(0), f"b{ctx.layer}")
-                dX = graph.aggregate(T, tag=f"b{ctx.layer}")
-                if gate_dx:  # the aggregation ends in an exchange or an accumulate: gate in a pass of its own
+                fused_gate = (gate_dx and X.is_contiguous() and getattr(graph, "fuses_gate", lambda F: False)(T.size(1)))
+                if fused_gate:  # the gate rides in the store of the aggregation's last launch
+                    dX = graph.aggregate(T, tag=f"b{ctx.layer}", gate=X)
+                else:
+                    dX = graph.aggregate(T, tag=f"b{ctx.layer}")
+                if gate_dx and not fused_gate:  # results that arrive through an exchange: gate in a pass of its own
                     dX = be.relu_backward(dX, X)
         return dX, None, dW, None, db, None, None, None, None
 

@@ -448,3 +448,36 @@ def test_layer_entry_points_of_the_c_abi(cuda, order, relu, recompute):
                                          Xg.data_ptr(), fin, Wg.data_ptr(), fout, None, flags, Y.data_ptr(), fout,
                                          None, AX.data_ptr(), fin, plan.buf.data_ptr(), plan.n_pieces, plan.n_slots,
                                          plan.n_cut, P, wsf.data_ptr(), 1024, s) == -4
+
+
+def test_padded_logits_gradient_flows_without_a_repadding_copy(cuda):
+    """256 -> 47 on enough rows to run padded to 48 columns, trained through the fused loss: the loss backward
+    writes its gradient with the logits' 48-float pitch and zero pad, the layer picks that buffer up as it is.
+    Gradients against the oracle model with torch's log_softmax + nll_loss."""
+    import graphcuda_b200 as gc
+    from graphcuda_b200 import engine, synth
+    from graphcuda_b200.models import GCN
+    n = 20_000
+    assert engine._padded_width(n, 256, 47) == 48
+    A = _graph(n, 12, seed=21)
+    X = synth.normal_features(n, 64, seed=22)
+    y = synth.uniform_labels(n, 47, seed=23)
+    dims = [64, 256, 47]
+    torch.manual_seed(4)
+    ref = O.GCN(dims)
+    torch.manual_seed(4)
+    model = GCN(dims).to(cuda)
+    out = ref(X, A)
+    torch.nn.functional.nll_loss(out, y).backward()
+    adj = gc.as_adjacency(A.to(cuda), symmetric=True)
+    logits = model(X.to(cuda), adj, log_softmax=False)
+    assert logits.shape == (n, 47) and logits.stride(0) == 48
+    loss = gc.log_softmax_nll_loss(logits, y.to(cuda))
+    seen = {}
+    logits.register_hook(lambda g: seen.setdefault("stride", g.stride()))
+    loss.backward()
+    assert seen["stride"] == (48, 1)  # the gradient arrived with the padded pitch
+    assert abs(float(loss) - float(torch.nn.functional.nll_loss(out, y))) < 1e-5
+    for conv, rconv in zip(model.convs, ref.convs):
+        assert O.rel_fro(conv.weights.grad, rconv.weights.grad) < 1e-3  # through a ReLU: rare tie flips
+    assert len(engine._zero_padded) <= 1  # the registry holds no buffer beyond the live gradient

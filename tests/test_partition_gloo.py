@@ -21,7 +21,7 @@ class TorchCPUBackend:
     def make_adj(self, rowptr, col, val, shape):
         return torch.sparse_csr_tensor(rowptr.long(), col.long(), val, size=tuple(shape))
 
-    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None):
+    def spmm(self, adj, H, *, bias=None, relu=False, accumulate_into=None, out=None, gate=None):
         y = adj @ H if adj.shape[0] and adj.shape[1] else torch.zeros(adj.shape[0], H.size(1))
         if accumulate_into is not None:
             y = accumulate_into + y
@@ -29,6 +29,8 @@ class TorchCPUBackend:
             y = y + bias
         if relu:
             y = y * (y > 0)
+        if gate is not None:
+            y = y * (gate > 0)
         if accumulate_into is not None:  # in place, like the CUDA kernel
             accumulate_into.copy_(y)
             return accumulate_into
