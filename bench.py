@@ -696,7 +696,7 @@ def run_ours(args):
             Xd, yd = feed.take()
             if overlap and i + 1 < k:
                 feed.submit([Xh, yh])
-            Xg = part.prepare_constant(Xd) if world > 1 else None
+            Xg = part.prepare_constant(Xd, keep=False) if world > 1 else None  # fresh inputs every step
             loss = step(Xd, yd, Xg)
             feed.release()
             float(loss.item())  # the device-to-host read of the result

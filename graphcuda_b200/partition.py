@@ -375,13 +375,15 @@ class PartitionedGraph:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
-    def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
+    def prepare_constant(self, X_local: torch.Tensor, keep: bool = True) -> torch.Tensor:
         """All rows of a matrix that does not change between steps (the input
-        features): gathered once, reused by every step."""
+        features): gathered once, reused by every step.  keep=False hands out
+        the exchange buffer itself, valid until the next call (inputs that are
+        refreshed every step)."""
         buf, work = self.all_gather_rows_async(X_local, tag="x")
         if work is not None:
             work.wait()
-        return buf.clone()
+        return buf.clone() if keep else buf
 
     # -- aggregation ----------------------------------------------------------
     def fuses_gate(self, F: int) -> bool:
@@ -561,10 +563,12 @@ class FeatureShardedGraph:
         self._push(pieces, hdl)
         return out[:self.rows, :F]
 
-    def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
+    def prepare_constant(self, X_local: torch.Tensor, keep: bool = True) -> torch.Tensor:
         """Column slab of a matrix that does not change between steps (the input
-        features): transposed once, reused by every step."""
-        return self.rows_to_columns(X_local, tag="x").clone()
+        features): transposed once, reused by every step (keep=False: the
+        exchange buffer itself, valid until the next call)."""
+        out = self.rows_to_columns(X_local, tag="x")
+        return out.clone() if keep else out
 
     # -- aggregation --------------------------------------------------------------
     def fuses_gate(self, F: int) -> bool:
@@ -639,8 +643,8 @@ class HybridGraph:
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
         return self.rows_graph.all_reduce_sum(t)
 
-    def prepare_constant(self, X_local: torch.Tensor) -> torch.Tensor:
-        return self.rows_graph.prepare_constant(X_local)
+    def prepare_constant(self, X_local: torch.Tensor, keep: bool = True) -> torch.Tensor:
+        return self.rows_graph.prepare_constant(X_local, keep)
 
     def out_slot(self, F: int, tag: str = "a"):
         return self.rows_graph.out_slot(F, tag) if self.scheme_for(F, False) == "rows" else None
