@@ -31,7 +31,6 @@
 #include "gemm_internal.cuh"
 
 #include <cuda.h>
-#include <cstdlib>
 
 namespace {
 
@@ -724,8 +723,6 @@ inline int64_t round8(int64_t x) { return (x + 7) & ~int64_t(7); }
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 int pick_bn(int64_t N) {
-  static const int force = [] { const char* e = getenv("GC_TC_FORCE_BN"); return e ? atoi(e) : 0; }();
-  if (force && N > 64) return force;
   if (N <= 64) return 64;
   if (N <= 128) return 128;
   const int64_t rem = N % 256;
