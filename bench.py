@@ -55,6 +55,9 @@ def parse():
                     help="multi-GPU scheme: adjacency rows (all-gather of the aggregated matrix), feature columns "
                          "(two transposes around the aggregation), or hybrid (rows for narrow and constant "
                          "matrices, feature slabs for the hidden width); auto = rows up to 4 GPUs, hybrid from 8")
+    ap.add_argument("--wide-from", type=int, default=128,
+                    help="hybrid scheme: matrices at least this wide are aggregated by feature slabs, narrower ones "
+                         "through the row partition")
     ap.add_argument("--exchange", default="auto", choices=["auto", "collective"],
                     help="auto: blocks move by peer copies through symmetric memory; collective: NCCL collectives")
     ap.add_argument("--no-parity", action="store_true",
@@ -568,7 +571,8 @@ def run_ours(args):
         if args.partition == "rows":
             part = PartitionedGraph(adj.rowptr, adj.col, adj.val, n, rank=rank, world=world, exchange=args.exchange)
         elif args.partition == "hybrid":
-            part = HybridGraph(adj.rowptr, adj.col, adj.val, adj, n, rank=rank, world=world, exchange=args.exchange)
+            part = HybridGraph(adj.rowptr, adj.col, adj.val, adj, n, rank=rank, world=world, exchange=args.exchange,
+                               wide_from=args.wide_from)
         else:
             part = FeatureShardedGraph(adj, n, rank=rank, world=world, exchange=args.exchange)
         lo, hi = part.lo, part.hi

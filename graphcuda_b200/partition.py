@@ -585,7 +585,8 @@ class FeatureShardedGraph:
             bp = self._buf(("bias", w, tag), (self.world * w,))  # zero-filled once; the tail beyond F stays zero
             bp[:F].copy_(bias)
             b_slab = bp[self.rank * w:(self.rank + 1) * w]
-        if self.symm is not None and self.world > 1 and hasattr(self.backend, "spmm_into_blocks"):
+        if (self.symm is not None and self.world > 1 and hasattr(self.backend, "spmm_into_blocks")
+                and not os.environ.get("GRAPHCUDA_B200_SEPARATE_C2R")):  # (the variable: for A/B measurements)
             return self._aggregate_into_owners(cols, F, w, b_slab, relu, tag)
         out = self._buf(("o", w, tag), (self.part.padded, w))
         self.backend.spmm(self.adj, cols[:self.n], bias=b_slab, relu=relu, out=out[:self.n])  # tail rows stay zero
