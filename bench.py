@@ -62,6 +62,8 @@ def parse():
                     help="auto: blocks move by peer copies through symmetric memory; collective: NCCL collectives")
     ap.add_argument("--no-parity", action="store_true",
                     help="skip the untimed CPU float64 check of the benchmarked graph's layers (profiler captures)")
+    ap.add_argument("--exchange-probe", action="store_true",
+                    help="time the multi-GPU block exchanges alone (peer memory against NCCL) instead of the step")
     ap.add_argument("--profile-warmup", action="store_true",
                     help="honour --warmup below 3 (profiler captures only; such a run is not a benchmark)")
     return ap.parse_args()
@@ -1044,8 +1046,75 @@ def reference_cuda_same_box(dev, full_graph=None):
     return out
 
 
+def run_exchange_probe(args):
+    """`--exchange-probe` (under torchrun, N >= 2): times the block exchanges of the partitioned layers by themselves,
+    on matrices of the workload's size -- the all-gather of row blocks pulled through symmetric memory against NCCL's
+    all_gather_into_tensor, and the rows -> columns transpose as one scatter kernel into the peers' buffers against
+    NCCL's all_to_all_single with its pack copy.  One JSON line from rank 0 (max over ranks)."""
+    import torch.distributed as dist
+
+    from graphcuda_b200.partition import FeatureShardedGraph, PartitionedGraph
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--exchange-probe needs at least two ranks (torchrun)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    n = workload(args.shrink)["nodes"]
+    empty = (torch.zeros(n + 1, dtype=torch.int32, device=dev), torch.empty(0, dtype=torch.int32, device=dev),
+             torch.empty(0, dtype=torch.float32, device=dev))
+    out = {"probe": "exchange", "n_gpus": world, "nodes": n}
+
+    def timed(fn, iters=5):
+        for _ in range(2):
+            fn()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for exch in ("auto", "collective"):
+        rows_g = PartitionedGraph(*empty, n, rank=rank, world=world, exchange=exch)
+        cols_g = FeatureShardedGraph(None, n, rank=rank, world=world, device=dev, exchange=exch)
+        name = "peer_memory" if rows_g.symm is not None else "nccl"
+        if exch == "auto" and rows_g.symm is None:
+            out["peer_memory"] = "symmetric memory unavailable"
+            continue
+        for F in (256, 48):
+            H = torch.randn(rows_g.rows, F, device=dev)
+
+            def gather():
+                _, work = rows_g.all_gather_rows_async(H, tag="p")
+                if work is not None:
+                    work.wait()
+
+            ms = timed(gather)
+            recv = (world - 1) * rows_g.part.block * F * 4
+            out[f"{name}_all_gather_F{F}"] = {"ms": ms, "GBs_in_per_rank": recv / ms / 1e6}
+            ms = timed(lambda: cols_g.rows_to_columns(H, tag="p"))
+            sent = (world - 1) * rows_g.part.block * cols_g.slab_width(F) * 4
+            out[f"{name}_rows_to_columns_F{F}"] = {"ms": ms, "GBs_out_per_rank": sent / ms / 1e6}
+        del rows_g, cols_g
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     args = parse()
+    if args.exchange_probe:
+        return run_exchange_probe(args)
     if args.impl == "reference":
         run_reference(args)
     else:
