@@ -785,6 +785,13 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_aux:
         try:
             line["aux"] = aux_measurements(dev, args)
+            # the F = 256 aggregation of the headline graph gathering a bf16 copy of H (reduced-precision tier)
+            from graphcuda_b200 import ops as _ops2
+            Hf = synth.normal_features(n, 256, seed=256, device=dev)
+            H16 = _ops2.to_bf16(Hf)
+            line["aux"]["rmat_products_spmm_F256_ms"] = {"fp32_H": _time_ms(lambda: adj.matmul(Hf), warm=2, iters=5),
+                                                         "bf16_H": _time_ms(lambda: adj.matmul(H16), warm=2, iters=5)}
+            del Hf, H16
             # the same training step in the opt-in reduced-precision tiers (1e-2 relative): not the headline
             for tier in ("tf32", "bf16"):
                 torch.manual_seed(0)
