@@ -171,7 +171,7 @@ def test_partitioned_model_matches_single_process(world, n, dims, mode, fuse):
     procs = [ctx.Process(target=_worker, args=(r, world, port, n, dims, q, mode, fuse, balance)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=120) for _ in range(world)]
+    results = [q.get(timeout=300) for _ in range(world)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
